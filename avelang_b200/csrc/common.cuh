@@ -1,0 +1,73 @@
+// Shared helpers for the GDN kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ave_gdn.h"
+
+namespace ave {
+
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return AVE_GDN_CUDA_ERROR;
+}
+
+#define AVE_CUDA_TRY(expr)                                   \
+  do {                                                       \
+    cudaError_t e__ = (expr);                                \
+    if (e__ != cudaSuccess) return ::ave::cuda_fail(e__);    \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+__device__ __forceinline__ void unpack_bf16x4(uint2 raw, float (&f)[4]) {
+  // bf16 -> fp32 is a 16-bit shift
+  f[0] = __uint_as_float(raw.x << 16);
+  f[1] = __uint_as_float(raw.x & 0xffff0000u);
+  f[2] = __uint_as_float(raw.y << 16);
+  f[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// Sequence n of a dense [B,T] batch or of a packed varlen batch: batch row, first token, length.
+struct SeqSpan {
+  int b;
+  int t0;
+  int len;
+  bool ok;
+};
+
+__device__ __forceinline__ SeqSpan seq_span(const int32_t* cu_seqlens, int n, int T, uint32_t* status) {
+  SeqSpan s;
+  if (cu_seqlens == nullptr) {
+    s.b = n; s.t0 = 0; s.len = T; s.ok = true;
+    return s;
+  }
+  const int a = cu_seqlens[n], e = cu_seqlens[n + 1];
+  s.b = 0; s.t0 = a; s.len = e - a;
+  s.ok = (a >= 0) && (e >= a) && (e <= T);
+  if (!s.ok) {
+    if (status != nullptr && threadIdx.x == 0) atomicOr(status, AVE_GDN_DEV_BAD_SEQLEN);
+    s.len = 0;
+  }
+  return s;
+}
+
+}  // namespace ave

@@ -1,0 +1,122 @@
+// Bandwidth-bound helpers around the recurrence: depthwise causal conv1d + SiLU, and the gate/beta math.
+#include "common.cuh"
+
+namespace ave {
+
+// One thread owns 8 adjacent channels (one 16-byte load per token) and walks a run of tokens with the
+// last width-1 inputs held in registers, so each input element is read from HBM once per run (+ halo).
+template <int WIDTH>
+__global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, int tokens_per_cta) {
+  const int cg = blockIdx.x * blockDim.x + threadIdx.x;  // channel group
+  if (cg * 8 >= a.C) return;
+  const int b = blockIdx.z;
+  const int t_begin = blockIdx.y * tokens_per_cta;
+  const int t_end = min(a.T, t_begin + tokens_per_cta);
+  if (t_begin >= t_end) return;
+  const __nv_bfloat16* xg = reinterpret_cast<const __nv_bfloat16*>(a.x) + b * a.x_stride_b + cg * 8;
+  __nv_bfloat16* yg = reinterpret_cast<__nv_bfloat16*>(a.y) + b * a.y_stride_b + cg * 8;
+
+  float w[8][WIDTH], bias[8];
+  {
+    const __nv_bfloat16* wg = reinterpret_cast<const __nv_bfloat16*>(a.w) + (int64_t)cg * 8 * WIDTH;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+#pragma unroll
+      for (int j = 0; j < WIDTH; ++j) w[c][j] = bf2f(wg[c * WIDTH + j]);
+      bias[c] = a.bias ? bf2f(reinterpret_cast<const __nv_bfloat16*>(a.bias)[cg * 8 + c]) : 0.f;
+    }
+  }
+  // sequence containing t_begin
+  int seq = 0, seq_start = 0, seq_end = a.T;
+  if (a.cu_seqlens != nullptr) {
+    int lo = 0, hi = a.n_seqs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.cu_seqlens[mid] <= t_begin) lo = mid; else hi = mid;
+    }
+    seq = lo; seq_start = a.cu_seqlens[seq]; seq_end = a.cu_seqlens[seq + 1];
+  }
+  auto load8 = [&](int t, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xg + (int64_t)t * a.x_stride_t);
+    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+    f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xffff0000u);
+    f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xffff0000u);
+  };
+  float hist[WIDTH][8];  // hist[WIDTH-1] is the current token
+#pragma unroll
+  for (int j = 0; j < WIDTH - 1; ++j) {
+    const int t = t_begin - (WIDTH - 1) + j;
+    if (t >= seq_start && t >= 0) {
+      load8(t, hist[j]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
+    }
+  }
+  for (int t = t_begin; t < t_end; ++t) {
+    if (a.cu_seqlens != nullptr && t >= seq_end) {  // crossed into the next sequence: forget history
+      while (t >= seq_end && seq + 1 < a.n_seqs) { ++seq; seq_start = seq_end; seq_end = a.cu_seqlens[seq + 1]; }
+#pragma unroll
+      for (int j = 0; j < WIDTH - 1; ++j)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
+    }
+    load8(t, hist[WIDTH - 1]);
+    float out[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float acc = bias[c];
+#pragma unroll
+      for (int j = 0; j < WIDTH; ++j) acc = fmaf(w[c][j], hist[j][c], acc);
+      out[c] = silu(acc);
+    }
+    uint4 packed = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]),
+                              pack_bf16x2(out[4], out[5]), pack_bf16x2(out[6], out[7]));
+    *reinterpret_cast<uint4*>(yg + (int64_t)t * a.y_stride_t) = packed;
+#pragma unroll
+    for (int j = 0; j < WIDTH - 1; ++j)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) hist[j][c] = hist[j + 1][c];
+  }
+}
+
+int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream) {
+  if (a.B == 0 || a.T == 0 || a.C == 0) return AVE_GDN_OK;
+  const int groups = a.C / 8;
+  const int threads = 128;
+  const int tokens_per_cta = 64;
+  dim3 grid((groups + threads - 1) / threads, (a.T + tokens_per_cta - 1) / tokens_per_cta, a.B);
+  switch (a.width) {
+    case 2: conv1d_silu_kernel<2><<<grid, threads, 0, stream>>>(a, tokens_per_cta); break;
+    case 3: conv1d_silu_kernel<3><<<grid, threads, 0, stream>>>(a, tokens_per_cta); break;
+    case 4: conv1d_silu_kernel<4><<<grid, threads, 0, stream>>>(a, tokens_per_cta); break;
+    default: return AVE_GDN_UNSUPPORTED;
+  }
+  AVE_CUDA_TRY(cudaGetLastError());
+  return AVE_GDN_OK;
+}
+
+__global__ void __launch_bounds__(256) gate_beta_kernel(const AveGateArgs a) {
+  const int64_t total = a.rows * a.Hv;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / a.Hv;
+    const int h = (int)(e - r * a.Hv);
+    const float av = bf2f(reinterpret_cast<const __nv_bfloat16*>(a.a)[r * a.a_stride_row + h]) + a.dt_bias[h];
+    const float bv = bf2f(reinterpret_cast<const __nv_bfloat16*>(a.b)[r * a.b_stride_row + h]);
+    const float sp = av > 20.f ? av : log1pf(expf(av));  // softplus
+    a.g[e] = -expf(a.A_log[h]) * sp;
+    a.beta[e] = 1.0f / (1.0f + expf(-bv));
+  }
+}
+
+int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream) {
+  const int64_t total = a.rows * a.Hv;
+  if (total == 0) return AVE_GDN_OK;
+  const int64_t blocks = (total + 255) / 256;
+  gate_beta_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, stream>>>(a);
+  AVE_CUDA_TRY(cudaGetLastError());
+  return AVE_GDN_OK;
+}
+
+}  // namespace ave

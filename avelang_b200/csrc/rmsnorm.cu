@@ -1,0 +1,91 @@
+// Gated RMSNorm over rows of d = 64 or 128 elements:  y = w * x * rsqrt(mean(x^2) + eps) * silu(z).
+// Pure streaming: one warp per row, 8-byte (d=128) or 4-byte (d=64) loads per lane, fp32 math.
+#include "common.cuh"
+
+namespace ave {
+
+template <int D, typename XT>
+__global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__ z,
+                                                            const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                            int64_t rows, int heads, int64_t xs_t, int64_t xs_h,
+                                                            int64_t zs_t, int64_t zs_h, int64_t ys_t, int64_t ys_h,
+                                                            float eps, int gate_first) {
+  constexpr int E = D / 32;  // elements per lane
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = warp_global; r < rows; r += n_warps) {
+    const int64_t t = r / heads;
+    const int h = (int)(r - t * heads);
+    const XT* xr = x + t * xs_t + h * xs_h + lane * E;
+    const __nv_bfloat16* zr = z + t * zs_t + h * zs_h + lane * E;
+    float xv[E], zv[E];
+    if constexpr (sizeof(XT) == 4) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) xv[i] = reinterpret_cast<const float*>(xr)[i];
+    } else if constexpr (E == 4) {
+      unpack_bf16x4(*reinterpret_cast<const uint2*>(xr), xv);
+    } else {
+      const uint32_t raw = *reinterpret_cast<const uint32_t*>(xr);
+      xv[0] = __uint_as_float(raw << 16); xv[1] = __uint_as_float(raw & 0xffff0000u);
+    }
+    if constexpr (E == 4) {
+      unpack_bf16x4(*reinterpret_cast<const uint2*>(zr), zv);
+    } else {
+      const uint32_t raw = *reinterpret_cast<const uint32_t*>(zr);
+      zv[0] = __uint_as_float(raw << 16); zv[1] = __uint_as_float(raw & 0xffff0000u);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      if (gate_first) xv[i] *= silu(zv[i]);
+      ss += xv[i] * xv[i];
+    }
+    ss = warp_sum(ss);
+    const float rinv = rsqrtf(ss * (1.0f / D) + eps);
+    float out[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float wv = w ? w[lane * E + i] : 1.0f;
+      out[i] = xv[i] * rinv * wv * (gate_first ? 1.0f : silu(zv[i]));
+    }
+    __nv_bfloat16* yr = y + t * ys_t + h * ys_h + lane * E;
+    if constexpr (E == 4) {
+      *reinterpret_cast<uint2*>(yr) = make_uint2(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]));
+    } else {
+      *reinterpret_cast<uint32_t*>(yr) = pack_bf16x2(out[0], out[1]);
+    }
+  }
+}
+
+template <typename XT>
+static int launch_norm_t(const XT* x, const AveGdnNormArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return AVE_GDN_OK;
+  const int64_t blocks_needed = (a.rows + 7) / 8;
+  const unsigned grid = (unsigned)(blocks_needed < 148 * 64 ? blocks_needed : 148 * 64);
+  const int gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) ? 1 : 0;
+  const __nv_bfloat16* z = reinterpret_cast<const __nv_bfloat16*>(a.z);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(a.y);
+  if (a.d == 128) {
+    gated_rmsnorm_kernel<128, XT><<<grid, 256, 0, stream>>>(x, z, a.weight, y, a.rows, a.heads, a.x_stride_t, a.x_stride_h,
+                                                            a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first);
+  } else if (a.d == 64) {
+    gated_rmsnorm_kernel<64, XT><<<grid, 256, 0, stream>>>(x, z, a.weight, y, a.rows, a.heads, a.x_stride_t, a.x_stride_h,
+                                                           a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first);
+  } else {
+    return AVE_GDN_UNSUPPORTED;
+  }
+  AVE_CUDA_TRY(cudaGetLastError());
+  return AVE_GDN_OK;
+}
+
+int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream) {
+  return launch_norm_t(reinterpret_cast<const __nv_bfloat16*>(a.x), a, stream);
+}
+
+// fp32 input variant used by the prefill path when the un-normalised output is staged in scratch
+int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream) {
+  return launch_norm_t(reinterpret_cast<const float*>(a.x), a, stream);
+}
+
+}  // namespace ave

@@ -1,0 +1,249 @@
+"""Gated-delta-net (GDN) linear attention for B200: chunked prefill, fused recurrent decode, gated RMSNorm.
+
+Entry points follow the calling convention of the reference's kernel library
+(python/avelang_kernels/amdgpu_gemm.py:458-494): plain module-level functions that take torch tensors,
+raise ValueError on dtype/shape/device problems, allocate the result unless ``out=`` is given, enqueue on
+torch's current stream of the tensors' device and return without synchronising.  The reference itself has
+no GDN kernels; the numerical contract is the recurrence
+
+    M <- exp(g_t) M;  r = M^T k_t;  u = beta_t (v_t - r);  M <- M + k_t u^T;  o_t = scale M^T q_t
+
+with M the fp32 key-major state [dk, dv] of one (sequence, value head).
+
+Layouts: q, k ``[B, T, Hk, dk]``; v, z, o ``[B, T, Hv, dv]``; g (log decay) and beta ``[B, T, Hv]`` fp32; value head
+h reads key head ``h // (Hv // Hk)``.  Varlen: ``B == 1`` and int32 ``cu_seqlens [N+1]`` on the device.  States:
+fp32 ``[N or num_slots, Hv, dk, dv]``.  The innermost dimension must be contiguous; head/token/batch strides
+are free as long as rows stay 16-byte aligned, so head-sharded slices of a packed tensor are accepted as is.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "read_status"]
+
+_status_words: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[idx]
+
+
+def read_status(device=None, reset: bool = True) -> int:
+    """Device status word accumulated by earlier calls (synchronises).  Bits: 1 = a state index beyond the
+    pool, 2 = malformed cu_seqlens, 4 = a bounded device wait gave up.  The affected sequences were skipped."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _status_word(device)
+    val = int(w.item())
+    if reset and val:
+        w.zero_()
+    return val
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch owned by the Python layer, grown on demand and reused (one per device and stream)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    cur = _workspaces.get(key)
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = cur
+    return cur
+
+
+def _req(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _check_common(q, k, v, g, beta, z, cu_seqlens):
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _req(isinstance(t, torch.Tensor) and t.dim() == 4, f"{name} must be a 4-D tensor [B, T, H, d]")
+        _req(t.dtype == torch.bfloat16, f"{name} must have dtype torch.bfloat16, got {t.dtype}.")
+        _req(t.is_cuda, f"{name} must be a CUDA tensor")
+        _req(t.stride(-1) == 1, f"{name} must be contiguous in its last dimension")
+        _req(t.device == q.device, f"{name} must be on device {q.device}, got {t.device}.")
+    B, T, Hk, dk = q.shape
+    _req(k.shape == q.shape, f"k must have shape {tuple(q.shape)}, got {tuple(k.shape)}.")
+    _req(v.shape[0] == B and v.shape[1] == T, f"v must have leading shape {(B, T)}, got {tuple(v.shape[:2])}.")
+    Hv, dv = v.shape[2], v.shape[3]
+    _req(Hv % Hk == 0, f"value heads ({Hv}) must be a multiple of key heads ({Hk}).")
+    _req((dk, dv) in ((128, 128), (64, 64)), f"head dims (dk, dv) must be (128, 128) or (64, 64), got {(dk, dv)}.")
+    for name, t in (("g", g), ("beta", beta)):
+        _req(t.dtype == torch.float32, f"{name} must have dtype torch.float32, got {t.dtype}.")
+        _req(tuple(t.shape) == (B, T, Hv), f"{name} must have shape {(B, T, Hv)}, got {tuple(t.shape)}.")
+        _req(t.device == q.device, f"{name} must be on device {q.device}, got {t.device}.")
+        _req(t.stride(-1) == 1 or Hv == 1, f"{name} must be contiguous in its last dimension")
+    _req(g.stride() == beta.stride(), "g and beta must share strides")
+    if z is not None:
+        _req(z.dtype == torch.bfloat16 and z.shape == v.shape and z.device == q.device and z.stride(-1) == 1,
+             f"z must be a bf16 tensor of shape {tuple(v.shape)} on {q.device}")
+    n_seqs = B
+    if cu_seqlens is not None:
+        _req(B == 1, "cu_seqlens requires B == 1 (packed layout)")
+        _req(cu_seqlens.dtype == torch.int32 and cu_seqlens.dim() == 1 and cu_seqlens.numel() >= 1,
+             "cu_seqlens must be a 1-D int32 tensor [N+1]")
+        _req(cu_seqlens.device == q.device and cu_seqlens.is_contiguous(), f"cu_seqlens must be contiguous on {q.device}")
+        n_seqs = cu_seqlens.numel() - 1
+    return B, T, Hk, Hv, dk, dv, n_seqs
+
+
+def _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final_state, cu_seqlens,
+               state_indices, num_slots, n_seqs, flags):
+    B, T, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    a = _lib.GdnArgs()
+    a.struct_size = ctypes.sizeof(_lib.GdnArgs)
+    a.flags = flags
+    ptr = lambda t: t.data_ptr() if t is not None and t.numel() > 0 else None
+    a.q, a.k, a.v, a.g, a.beta, a.z, a.o = ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(z), ptr(o)
+    a.norm_weight = ptr(norm_weight)
+    a.initial_state, a.final_state = ptr(initial_state), ptr(final_state)
+    a.cu_seqlens, a.state_indices = ptr(cu_seqlens), ptr(state_indices)
+    a.status = _status_word(q.device).data_ptr()
+    a.B, a.T, a.Hk, a.Hv, a.dk, a.dv = B, T, Hk, Hv, dk, dv
+    a.n_seqs, a.num_slots, a.chunk = n_seqs, num_slots, 64
+    for name, t in (("q", q), ("k", k), ("v", v), ("z", z), ("o", o)):
+        if t is not None:
+            setattr(a, f"{name}_stride_b", t.stride(0))
+            setattr(a, f"{name}_stride_t", t.stride(1))
+            setattr(a, f"{name}_stride_h", t.stride(2))
+    a.g_stride_b, a.g_stride_t = g.stride(0), g.stride(1)
+    a.scale = float(dk ** -0.5 if scale is None else scale)
+    a.norm_eps = float(norm_eps)
+    return a
+
+
+def _prep_out(out, v, z):
+    if out is None:
+        return torch.empty(v.shape, dtype=torch.bfloat16, device=v.device)
+    _req(out.shape == v.shape, f"out must have shape {tuple(v.shape)}, got {tuple(out.shape)}.")
+    _req(out.dtype == torch.bfloat16, f"out must have dtype torch.bfloat16, got {out.dtype}.")
+    _req(out.device == v.device, f"out must be on device {v.device}, got {out.device}.")
+    _req(out.stride(-1) == 1, "out must be contiguous in its last dimension")
+    return out
+
+
+def _prep_norm_weight(norm_weight, z, dv, device):
+    if norm_weight is None:
+        return None
+    _req(z is not None, "norm_weight needs z (the gate of the fused RMSNorm)")
+    _req(norm_weight.numel() == dv and norm_weight.device == device, f"norm_weight must have {dv} elements on {device}")
+    return norm_weight.detach().float().contiguous()
+
+
+def _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, device, want_final, inplace):
+    num_slots = n_seqs
+    if initial_state is not None:
+        _req(initial_state.dtype == torch.float32, f"initial_state must have dtype torch.float32, got {initial_state.dtype}.")
+        _req(initial_state.dim() == 4 and tuple(initial_state.shape[1:]) == (Hv, dk, dv),
+             f"initial_state must have shape [N, {Hv}, {dk}, {dv}], got {tuple(initial_state.shape)}.")
+        _req(initial_state.is_contiguous() and initial_state.device == device, f"initial_state must be contiguous on {device}")
+        num_slots = initial_state.shape[0]
+    if state_indices is not None:
+        _req(initial_state is not None, "state_indices needs initial_state (the state pool)")
+        _req(state_indices.dtype == torch.int32 and tuple(state_indices.shape) == (n_seqs,),
+             f"state_indices must be int32 of shape ({n_seqs},)")
+        _req(state_indices.device == device and state_indices.is_contiguous(), f"state_indices must be contiguous on {device}")
+    else:
+        _req(initial_state is None or num_slots == n_seqs,
+             f"initial_state must hold one state per sequence ({n_seqs}), got {num_slots}.")
+    final = None
+    if want_final:
+        if state_indices is not None and inplace:
+            final = initial_state
+        elif state_indices is not None:
+            final = initial_state.clone()
+        else:
+            final = torch.empty(n_seqs, Hv, dk, dv, dtype=torch.float32, device=device)
+    return final, num_slots
+
+
+def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, *, z=None, norm_weight=None,
+                           norm_eps=1e-6, state_indices=None, inplace_state=True, chunk_size=64, out=None):
+    """Chunked (chunk 64) gated delta rule over whole sequences.  Returns ``(o, final_state or None)``.
+
+    With ``z`` the gated RMSNorm ``rmsnorm(o) * silu(z)`` (weight ``norm_weight``, eps ``norm_eps``) is fused and
+    ``o`` is the normalised output.  With ``state_indices`` the initial states are read from, and the final
+    states written to, slots of the ``initial_state`` pool (in place unless ``inplace_state=False``)."""
+    B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, z, cu_seqlens)
+    _req(chunk_size == 64, f"chunk_size must be 64, got {chunk_size}.")
+    o = _prep_out(out, v, z)
+    norm_weight = _prep_norm_weight(norm_weight, z, dv, q.device)
+    final, num_slots = _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, q.device,
+                                    output_final_state, inplace_state)
+    flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
+    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
+                   state_indices, num_slots, n_seqs, flags)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        nbytes = lib.ave_gdn_prefill_workspace_bytes(ctypes.byref(a))
+        ws = _workspace(q.device, nbytes)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        rc = lib.ave_gdn_chunk_prefill(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "chunk_gated_delta_rule")
+    return o, final
+
+
+def fused_recurrent_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
+                                     use_qk_l2norm_in_kernel=False, cu_seqlens=None, *, state_indices=None,
+                                     inplace_state=True, z=None, norm_weight=None, norm_eps=1e-6, out=None):
+    """Token-by-token gated delta rule with the state tile held on chip; ``T == 1`` with ``state_indices`` is the
+    continuous-batching decode step: each sequence's state is streamed once in and once out of its slot of the
+    ``initial_state`` pool (updated in place unless ``inplace_state=False``).  A negative slot index skips the
+    sequence (no state access, zero output).  Returns ``(o, state)``."""
+    B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, z, cu_seqlens)
+    o = _prep_out(out, v, z)
+    norm_weight = _prep_norm_weight(norm_weight, z, dv, q.device)
+    final, num_slots = _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, q.device,
+                                    output_final_state, inplace_state)
+    flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
+    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
+                   state_indices, num_slots, n_seqs, flags)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().ave_gdn_decode_step(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "fused_recurrent_gated_delta_rule")
+    return o, final
+
+
+def gated_rmsnorm(x, z, weight=None, eps=1e-6, *, gate_first=False, out=None):
+    """``y = weight * x * rsqrt(mean(x^2) + eps) * silu(z)`` over the last dimension (64 or 128), bf16 in/out,
+    fp32 math.  ``x``/``z``/``out``: ``[..., H, d]`` with a contiguous last dimension."""
+    _req(x.dtype == torch.bfloat16, f"x must have dtype torch.bfloat16, got {x.dtype}.")
+    _req(z.dtype == torch.bfloat16, f"z must have dtype torch.bfloat16, got {z.dtype}.")
+    _req(x.is_cuda and z.device == x.device, f"z must be on device {x.device}, got {z.device}.")
+    _req(z.shape == x.shape, f"z must have shape {tuple(x.shape)}, got {tuple(z.shape)}.")
+    _req(x.dim() >= 2 and x.shape[-1] in (64, 128), f"last dimension must be 64 or 128, got {x.shape[-1]}.")
+    d, H = x.shape[-1], x.shape[-2]
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _req(out.shape == x.shape and out.dtype == torch.bfloat16 and out.device == x.device,
+         f"out must be a bf16 tensor of shape {tuple(x.shape)} on {x.device}")
+    x3, z3, y3 = (t.reshape(-1, H, d) if t.dim() != 3 else t for t in (x, z, out))
+    _req(y3.data_ptr() == out.data_ptr(), "out must be viewable as [rows, H, d] without a copy")
+    for t in (x3, z3, y3):
+        _req(t.stride(-1) == 1, "tensors must be contiguous in their last dimension")
+    a = _lib.NormArgs()
+    a.struct_size = ctypes.sizeof(_lib.NormArgs)
+    a.flags = _lib.FLAG_GATE_FIRST if gate_first else 0
+    a.x, a.z, a.y = x3.data_ptr(), z3.data_ptr(), y3.data_ptr()
+    w = None
+    if weight is not None:
+        _req(weight.numel() == d and weight.device == x.device, f"weight must have {d} elements on {x.device}")
+        w = weight.detach().float().contiguous()
+        a.weight = w.data_ptr()
+    a.rows, a.d, a.heads, a.eps = x3.shape[0] * H, d, H, float(eps)
+    a.x_stride_t, a.x_stride_h = x3.stride(0), x3.stride(1)
+    a.z_stride_t, a.z_stride_h = z3.stride(0), z3.stride(1)
+    a.y_stride_t, a.y_stride_h = y3.stride(0), y3.stride(1)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().ave_gdn_gated_rmsnorm(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "gated_rmsnorm")
+    return out

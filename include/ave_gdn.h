@@ -1,0 +1,171 @@
+/* C ABI of libave_gdn_b200.so: gated-delta-net (GDN) linear-attention kernels for NVIDIA B200 (sm_100a).
+ *
+ * The reference project (848267592/avelang) ships kernel libraries as Python functions in the
+ * `avelang_kernels` namespace that take torch tensors, validate them, allocate the output unless `out=`
+ * is given, launch on the current stream and never synchronise
+ * (python/avelang_kernels/amdgpu_gemm.py:458-494).  Under that convention each kernel is reached through
+ * a generated per-signature C launcher, `launch(gx,gy,gz,bx,by,bz,stream,func,*args)`
+ * (python/avelang/backends/nvidia/driver.py:182-312), which pulls `data_ptr()` out of every tensor,
+ * rejects host pointers and enqueues with cuLaunchKernel.  The entry points below take the place of that
+ * launcher for the GDN path: plain device pointers, sizes and element strides in, one status code out.
+ * The reference has no GDN kernels of its own; `ave_gemm_bf16_nt` is the only entry point with a direct
+ * counterpart (gemm_pipeline_transposed_b, amdgpu_gemm.py:458-494).
+ *
+ * Conventions
+ *  - Every pointer is a device pointer on the current CUDA device unless stated; the caller owns all
+ *    buffers, including workspace.  No entry point allocates device memory or synchronises the device.
+ *  - `stream` is a cudaStream_t passed as void*.  A call enqueues a fixed sequence of kernels on it.
+ *  - Strides are in ELEMENTS.  The innermost (head-feature) dimension must be contiguous and every row
+ *    16-byte aligned.
+ *  - Return value: AVE_GDN_OK or an AveGdnStatus code.  Nothing aborts or throws across the boundary.
+ *  - Data-dependent faults (a slot index outside the pool, a bounded device wait that ran out) cannot be
+ *    seen by the host without a sync: the kernels skip the offending unit and OR a bit into the optional
+ *    device word `status` (see AVE_GDN_DEV_*).
+ *  - Tensor roles: q,k [B,T,Hk,dk]; v,z,o [B,T,Hv,dv]; g (log decay, <= 0) and beta [B,T,Hv] fp32;
+ *    value head h reads key head h / (Hv/Hk).  State tiles are fp32 [dk][dv], key-major:
+ *    o_t = scale * M^T q_t,   M <- exp(g_t) M + k_t (beta_t (v_t - exp(g_t) M^T k_t))^T.
+ */
+#ifndef AVE_GDN_H_
+#define AVE_GDN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AVE_GDN_ABI_VERSION 1
+
+typedef enum AveGdnStatus {
+  AVE_GDN_OK = 0,
+  AVE_GDN_INVALID_ARGUMENT = 1, /* null pointer, negative size, struct_size mismatch */
+  AVE_GDN_UNSUPPORTED = 2,      /* shape outside what the kernels are built for */
+  AVE_GDN_MISALIGNED = 3,       /* pointer or stride breaks the 16-byte rule */
+  AVE_GDN_CUDA_ERROR = 4,       /* see ave_gdn_last_cuda_error() */
+  AVE_GDN_WORKSPACE_TOO_SMALL = 5
+} AveGdnStatus;
+
+/* bits OR-ed into the device status word */
+#define AVE_GDN_DEV_BAD_SLOT 1u      /* state index >= num_slots: that sequence was skipped */
+#define AVE_GDN_DEV_BAD_SEQLEN 2u    /* cu_seqlens not monotone or beyond T: that sequence was skipped */
+#define AVE_GDN_DEV_WAIT_EXPIRED 4u  /* a bounded wait inside a kernel gave up */
+
+/* flags */
+#define AVE_GDN_FLAG_QK_L2NORM 1u    /* normalise q and k per head vector (eps 1e-6) inside the kernel */
+#define AVE_GDN_FLAG_GATE_FIRST 2u   /* gated norm computes rmsnorm(o * silu(z)) instead of rmsnorm(o) * silu(z) */
+
+/* One argument block for both recurrences (chunked prefill and token-by-token decode). */
+typedef struct AveGdnArgs {
+  uint32_t struct_size; /* sizeof(AveGdnArgs), checked */
+  uint32_t flags;
+  const void* q; /* bf16 */
+  const void* k; /* bf16 */
+  const void* v; /* bf16 */
+  const float* g;
+  const float* beta;
+  const void* z;             /* bf16, optional: fuses the gated RMSNorm into the output */
+  const float* norm_weight;  /* fp32 [dv], optional (unit weight when null) */
+  void* o;                   /* bf16 */
+  const float* initial_state; /* optional (zero state when null) */
+  float* final_state;         /* optional (not written when null); may alias initial_state */
+  const int32_t* cu_seqlens;    /* optional int32 [n_seqs+1]; requires B == 1 */
+  const int32_t* state_indices; /* optional int32 [n_seqs]: sequence n uses state tile state_indices[n]
+                                   of initial_state/final_state (negative: skip the sequence, o = 0) */
+  uint32_t* status;           /* optional device status word */
+  void* workspace;            /* device scratch, >= ave_gdn_prefill_workspace_bytes(); prefill only */
+  uint64_t workspace_bytes;
+  int32_t B, T, Hk, Hv, dk, dv;
+  int32_t n_seqs;    /* B when cu_seqlens is null */
+  int32_t num_slots; /* tiles in the state arrays; n_seqs when state_indices is null */
+  int32_t chunk;     /* prefill: 64 */
+  int32_t reserved0;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  int64_t z_stride_b, z_stride_t, z_stride_h;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  int64_t g_stride_b, g_stride_t; /* g and beta share strides; head stride is 1 */
+  float scale;
+  float norm_eps;
+} AveGdnArgs;
+
+/* Chunked prefill (chunk 64, WY/UT form), dense [B,T] or packed varlen via cu_seqlens. */
+int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream);
+size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args);
+
+/* Token-by-token recurrence with the state tile held on chip; T == 1 with state_indices is the
+ * continuous-batching decode step (state streamed once in, once out, updated in place). */
+int ave_gdn_decode_step(const AveGdnArgs* args, void* stream);
+
+/* y = w * x * rsqrt(mean(x^2) + eps) * silu(z) over rows of `d` elements. */
+typedef struct AveGdnNormArgs {
+  uint32_t struct_size;
+  uint32_t flags;        /* AVE_GDN_FLAG_GATE_FIRST */
+  const void* x;         /* bf16 */
+  const void* z;         /* bf16 */
+  const float* weight;   /* fp32 [d], optional */
+  void* y;               /* bf16 */
+  int64_t rows;          /* number of (token, head) rows */
+  int32_t d;             /* 64 or 128 */
+  int32_t heads;         /* rows are indexed (token, head) = (r / heads, r % heads) */
+  int64_t x_stride_t, x_stride_h, z_stride_t, z_stride_h, y_stride_t, y_stride_h;
+  float eps;
+  float reserved0;
+} AveGdnNormArgs;
+int ave_gdn_gated_rmsnorm(const AveGdnNormArgs* args, void* stream);
+
+/* C[M,N] = A[M,K] * B[N,K]^T, bf16 in/out, fp32 accumulate: the operand convention of
+ * gemm_pipeline_transposed_b (python/avelang_kernels/amdgpu_gemm.py:458-494). */
+typedef struct AveGemmArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* a;
+  const void* b;
+  void* c;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc; /* row strides in elements, multiples of 8 */
+} AveGemmArgs;
+int ave_gemm_bf16_nt(const AveGemmArgs* args, void* stream);
+
+/* Depthwise causal conv over time (kernel width 2..4) followed by SiLU, zero history at each sequence
+ * start.  x,y [B,T,C] bf16, w [C,width] bf16, optional bias [C] bf16, optional cu_seqlens (B == 1). */
+typedef struct AveConvArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* x;
+  const void* w;
+  const void* bias;
+  void* y;
+  const int32_t* cu_seqlens;
+  int32_t B, T, C, width, n_seqs, reserved0;
+  int64_t x_stride_b, x_stride_t, y_stride_b, y_stride_t;
+} AveConvArgs;
+int ave_gdn_conv1d_silu(const AveConvArgs* args, void* stream);
+
+/* g = -exp(A_log[h]) * softplus(a + dt_bias[h]),  beta = sigmoid(b);  a,b bf16 [rows,Hv] (strided),
+ * A_log,dt_bias fp32 [Hv];  g,beta fp32 [rows,Hv] contiguous. */
+typedef struct AveGateArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* a;
+  const void* b;
+  const float* A_log;
+  const float* dt_bias;
+  float* g;
+  float* beta;
+  int64_t rows;
+  int32_t Hv, reserved0;
+  int64_t a_stride_row, b_stride_row;
+} AveGateArgs;
+int ave_gdn_gate_beta(const AveGateArgs* args, void* stream);
+
+int ave_gdn_abi_version(void);
+const char* ave_gdn_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made by this thread through the library (0 if none). */
+int ave_gdn_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AVE_GDN_H_ */
