@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the GDN hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one chunked prefill of the Qwen3-Next GDN layer workload (B=1 per GPU, T=8192, 16 key / 32 value
+heads, d=128, bf16 q/k/v/z, fp32 g/beta, fused gated RMSNorm, fp32 final state).  With N GPUs every rank owns
+one such sequence (the path is partitioned by (sequence, value head); there is no collective in the
+recurrence), so the job is N sequences and `value` is their total tokens per second: weak scaling.  Under
+torchrun each rank reads RANK/LOCAL_RANK/WORLD_SIZE; rank 0 prints ONE JSON line.
+
+Extra objects on the same line: `decode` (continuous-batch decode step over a 512-slot fp32 state pool: state
+GB/s against the HBM roofline), `roofline`, `cpu_baseline`, `e2e`, `clocks`.
+`--impl reference` times the CPU restatement of the recurrence on the host cores instead (the reference
+project has no implementation of this path, so the restatement is the only CPU arm there is).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FLOP_PER_CHUNK_HEAD = 10_485_760  # 8 dense contractions of the chunked form, K K^T and Q K^T shared by 2 value heads
+T_PREFILL, HK, HV, D = 8192, 16, 32, 128
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, warmup, world, flush):
+    """W untimed warm-ups, then K steps each bracketed by its own CUDA event pair on the launching stream,
+    with an L2 flush (untimed) between them; returns total milliseconds of the K steps."""
+    for _ in range(warmup):
+        fn()
+    barrier(world)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush.add_(1.0)  # 256 MiB write: larger than the 126 MB L2
+        a.record()
+        fn()
+        b.record()
+    barrier(world)
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+def bench_prefill(args, rank, world):
+    from avelang_b200 import gdn, synth
+    inp = synth.config1(seed=rank)
+    g = inp.to("cuda")
+    out = torch.empty_like(g.v)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+
+    def step():
+        return gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, output_final_state=True, z=g.z, out=out)
+
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        total_ms = time_steps(step, args.steps, args.warmup, world, flush)
+    total_ms = max_over_ranks(total_ms, world)
+    ms = total_ms / args.steps
+
+    # end to end: pinned host buffers -> device -> kernel -> host, every step
+    host = {k: getattr(inp, k).pin_memory() for k in ("q", "k", "v", "z", "g", "beta")}
+    dev = {k: torch.empty_like(getattr(g, k)) for k in host}
+    o_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    s_host = torch.empty(1, HV, D, D, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        for k in host:
+            dev[k].copy_(host[k], non_blocking=True)
+        o, s = gdn.chunk_gated_delta_rule(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], output_final_state=True,
+                                          z=dev["z"], out=out)
+        o_host.copy_(o, non_blocking=True)
+        s_host.copy_(s, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier(world)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1) / e2e_steps, world)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = o_host.numel() * o_host.element_size() + s_host.numel() * s_host.element_size()
+    return ms, clocks.summary(), e2e_ms, h2d, d2h
+
+
+def bench_decode(steps=1000, warmup=20):
+    """256 sequences x 32 heads, one token each, state pool of 512 fp32 slots updated in place; a ring of 8
+    pre-generated q/k/v/g/beta sets so the small inputs are not replayed from cache."""
+    from avelang_b200 import gdn, synth
+    base = synth.config2().to("cuda")
+    ring = [synth.config2(seed=100 + i).to("cuda") for i in range(8)]
+    pool, idx = base.state_pool, base.state_indices
+    out = torch.empty_like(base.v)
+
+    def step(i):
+        r = ring[i % 8]
+        gdn.fused_recurrent_gated_delta_rule(r.q, r.k, r.v, r.g, r.beta, initial_state=pool, state_indices=idx, out=out)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / steps
+    state_bytes = 256 * HV * D * D * 4 * 2
+    other = 256 * (HK * D * 2 * 2 + HV * D * 2 * 2 + HV * 4 * 2 + 4)
+    return us, state_bytes, state_bytes + other
+
+
+def cpu_baseline(sample_tokens=T_PREFILL, reps=3):
+    """The C restatement of the token recurrence (fp32, OpenMP over sequence x head) on the host cores."""
+    from avelang_b200 import synth
+    from oracle import c_oracle
+    inp = synth.config1(T=sample_tokens)
+    times = []
+    for _ in range(reps):
+        t = time.perf_counter()
+        c_oracle.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, precision="f32")
+        times.append(time.perf_counter() - t)
+    sec = statistics.median(times)
+    return {"value": sample_tokens / sec, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"full workload (T={sample_tokens}, 32 value heads, d=128), fp32 token recurrence in C with "
+                      f"OpenMP, median of {reps} runs, {sec:.3f} s each"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(reps=1)
+    t = time.perf_counter()
+    base = cpu_baseline(reps=max(1, min(args.steps, 5)))
+    wall = time.perf_counter() - t
+    line = {"impl": "reference", "metric": "gdn_prefill_tokens_per_s", "value": base["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * T_PREFILL / base["value"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus), "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": f"CPU restatement of the recurrence (the reference ships no GDN code); wall {wall:.1f} s"}
+    print(json.dumps(line))
+
+
+def workload_config(n):
+    return {"workload": "qwen3-next-80b-a3b GDN layer chunked prefill, B=1 per GPU, T=8192, Hk=16, Hv=32, d=128, "
+                        "chunk 64, bf16 q/k/v/z, fp32 g/beta, fused gated RMSNorm, fp32 final state",
+            "global_batch": n, "seq_len": T_PREFILL, "parallelism": f"sequence-sharded x{n}, no collective",
+            "l2": "256 MiB flush write before every timed step; inputs 272 MB > 126 MB L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    from avelang_b200 import _lib
+    _lib.load()  # fail loudly when the CUDA library is missing
+    rank, world, local = dist_setup(args.gpus)
+    peaks = measured_peaks()
+
+    ms, clocks, e2e_ms, h2d, d2h = bench_prefill(args, rank, world)
+    tokens = T_PREFILL * world
+    flops = (T_PREFILL // 64) * HV * FLOP_PER_CHUNK_HEAD
+    algo_bytes = 272_629_760
+    line = {"metric": "gdn_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 in / fp32 state and accumulate", "data": "synthetic",
+            "config": workload_config(world),
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": 3 * args.steps, "clocks": clocks}
+    achieved = flops / (ms * 1e-3) / 1e12
+    line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                        "peak_source": peaks["source"] + " (burst)",
+                        "note": "algorithmic 42.95 GFLOP per step over the whole step (all launches): a lower bound "
+                                "for the dominant kernel",
+                        "hbm_view": {"achieved_gbs": algo_bytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                                     "algorithmic_bytes": algo_bytes}}
+    if rank == 0 and not args.no_decode:
+        us, state_bytes, all_bytes = bench_decode()
+        line["decode"] = {"metric": "gdn_decode_state_GBps", "value": state_bytes / (us * 1e-6) / 1e9, "unit": "GB/s",
+                          "us_per_step": us, "steps": 1000,
+                          "config": {"workload": "256 seqs x 32 value heads, T=1, 512-slot fp32 pool [128x128], in place"},
+                          "roofline": {"bound": "hbm", "achieved": all_bytes / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
+                                       "unit": "GB/s", "frac": all_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
+                                       "frac_of_nominal_8TBps": all_bytes / (us * 1e-6) / 8e12, "traffic": None,
+                                       "peak_source": peaks["source"]}}
+    if world > 1:
+        barrier(world)
+    if rank == 0:
+        if not args.no_cpu and world == 1:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
