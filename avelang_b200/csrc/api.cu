@@ -8,10 +8,16 @@ thread_local int g_last_cuda_error = 0;
 int launch_decode(const AveGdnArgs& a, cudaStream_t stream);
 int launch_prefill_simt(const AveGdnArgs& a, cudaStream_t stream);
 size_t prefill_simt_workspace_bytes(const AveGdnArgs& a);
+int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream);
+size_t prefill_tc_workspace_bytes(const AveGdnArgs& a);
 int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream);
 int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
+
+static size_t prefill_ws_bytes(const AveGdnArgs& a) {
+  return a.dk == 128 ? prefill_tc_workspace_bytes(a) : prefill_simt_workspace_bytes(a);
+}
 
 static int check_rows(const void* p, int64_t st, int64_t sh, int64_t sb, int elem_bytes) {
   if (!aligned16(p)) return AVE_GDN_MISALIGNED;
@@ -65,7 +71,7 @@ const char* ave_gdn_status_string(int status) {
 
 size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args) {
   if (validate_gdn(args, true) != AVE_GDN_OK) return 0;
-  return prefill_simt_workspace_bytes(*args);
+  return prefill_ws_bytes(*args);
 }
 
 int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream) {
@@ -73,7 +79,9 @@ int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream) {
   if (rc != AVE_GDN_OK) return rc;
   if ((int64_t)args->B * args->T == 0 || args->n_seqs == 0) return AVE_GDN_OK;
   if (args->workspace == nullptr || !aligned16(args->workspace)) return AVE_GDN_INVALID_ARGUMENT;
-  if (args->workspace_bytes < prefill_simt_workspace_bytes(*args)) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  if (args->workspace_bytes < prefill_ws_bytes(*args)) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  // d = 128 runs on the tensor cores; d = 64 (the small CPU-reference shape) on the fp32 CUDA-core kernels
+  if (args->dk == 128) return launch_prefill_tc(*args, reinterpret_cast<cudaStream_t>(stream));
   return launch_prefill_simt(*args, reinterpret_cast<cudaStream_t>(stream));
 }
 
