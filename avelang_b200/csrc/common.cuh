@@ -44,7 +44,7 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // Sequence n of a dense [B,T] batch or of a packed varlen batch: batch row, first token, length.
 struct SeqSpan {

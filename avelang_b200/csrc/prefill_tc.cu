@@ -73,68 +73,101 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bflo
   lo = __float2bfloat16(x - __bfloat162float(hi));
 }
 
-// 64x64 = A(64xD) * B(64xD)^T over a 256-thread CTA, both operands row-major with leading dimension ld.
-template <class Epi>
-__device__ __forceinline__ void gram64(const float* __restrict__ A, const float* __restrict__ B, int ld, Epi epi) {
-  const int tid = threadIdx.x, tj = tid % 32, ti = tid / 32;
-  float acc[8][2];
-#pragma unroll
-  for (int x = 0; x < 8; ++x) { acc[x][0] = 0.f; acc[x][1] = 0.f; }
-#pragma unroll 4
-  for (int d = 0; d < D; ++d) {
-    const float b0 = B[tj * ld + d], b1 = B[(tj + 32) * ld + d];
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const float av = A[(ti + x * 8) * ld + d];
-      acc[x][0] = fmaf(av, b0, acc[x][0]);
-      acc[x][1] = fmaf(av, b1, acc[x][1]);
-    }
-  }
-#pragma unroll
-  for (int x = 0; x < 8; ++x) { epi(ti + x * 8, tj, acc[x][0]); epi(ti + x * 8, tj + 32, acc[x][1]); }
-}
+struct GdnMaps {
+  CUtensorMap q, k, v, w_hi, w_lo, p_hi, p_lo;
+};
 
-__global__ void __launch_bounds__(256) chunk_prep_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, PrepOut out) {
-  constexpr int LDK = D + 1;
-  extern __shared__ __align__(16) float smem_f[];
-  float* Ks = smem_f;
-  float* Qs = Ks + C * LDK;
-  float* As = Qs + C * LDK;      // [64][65]
-  float* bs = As + C * (C + 1);
+// ------------------------------------------------------------------------------------------------ pass 1
+// Shared memory of chunk_prep (offsets from a 1024-byte aligned base).  The K and Q tiles are interleaved by
+// 64-wide halves, [K_h0 | Q_h0 | K_h1 | Q_h1], so that one M = 128 MMA reads [K; Q] as its A operand (rows 0..63 =
+// K, 64..127 = Q) and the K rows alone as its N = 64 B operand: lanes 0..63 of the accumulator are K K^T, lanes
+// 64..127 are Q K^T.
+constexpr int PREP_THREADS = 256;
+constexpr int PP_KQ = 0, PP_V = 32768, PP_A = 49152, PP_SC = PP_A + C * (C + 1) * 4, PP_BARS = PP_SC + 4 * C * 4;
+constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
+
+__global__ void __launch_bounds__(PREP_THREADS, 2)
+chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][65]
+  float* bs = reinterpret_cast<float*>(smem + PP_SC);
   float* betas = bs + C;
   float* qn = betas + C;
   float* kn = qn + C;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_BARS);
+  uint64_t* tma_bar = bars;
+  uint64_t* mma_bar = bars + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
   const ChunkRef cr = find_chunk(a, chunk_start, c);
   if (!cr.ok) return;
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
-  const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(a.q) + cr.b * a.q_stride_b + (int64_t)hk * a.q_stride_h;
-  const __nv_bfloat16* kg = reinterpret_cast<const __nv_bfloat16*>(a.k) + cr.b * a.k_stride_b + (int64_t)hk * a.k_stride_h;
-  const __nv_bfloat16* vg = reinterpret_cast<const __nv_bfloat16*>(a.v) + cr.b * a.v_stride_b + (int64_t)h * a.v_stride_h;
 
-  for (int e = tid; e < C * D; e += 256) {
-    const int i = e / D, d = e % D;
-    float kv = 0.f, qv = 0.f;
-    if (i < cr.len) {
-      kv = bf2f(kg[(int64_t)(cr.t0 + i) * a.k_stride_t + d]);
-      qv = bf2f(qg[(int64_t)(cr.t0 + i) * a.q_stride_t + d]);
-    }
-    Ks[i * LDK + d] = kv; Qs[i * LDK + d] = qv;
+  if (tid == 0) {
+    tc::mbar_init(tma_bar, 1);
+    tc::mbar_init(mma_bar, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::mbar_expect_tx(tma_bar, 32768 + 16384);
+    tc::tma_load_4d(smem + PP_KQ, &maps.k, tma_bar, 0, hk, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_KQ + 8192, &maps.q, tma_bar, 0, hk, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_KQ + 16384, &maps.k, tma_bar, 64, hk, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_KQ + 24576, &maps.q, tma_bar, 64, hk, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
   }
+  if (warp == 0) tc::tmem_alloc(tmem_slot, 64);
   if (tid < C) {
     const bool valid = tid < cr.len;
     const int64_t off = cr.b * a.g_stride_b + (int64_t)(cr.t0 + tid) * a.g_stride_t + h;
     bs[tid] = valid ? a.g[off] : 0.f;
     betas[tid] = valid ? a.beta[off] : 0.f;
   }
+  tc::tc_fence_before_sync();
   __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tm = *tmem_slot;
   if (tid == 0) { float run = 0.f; for (int i = 0; i < C; ++i) { run += bs[i]; bs[i] = run; } }
+
+  bool ok = tc::mbar_wait(tma_bar, 0, abort_flag);
+  if (warp == 0) {
+    tc::tc_fence_after_sync();
+    const bool leader = tc::elect_one();
+    if (ok && leader) {
+      constexpr uint32_t idesc = tc::idesc_f16(128, 64, 1, 1, false, false);
+      const uint32_t base = tc::smem_u32(smem + PP_KQ);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint64_t d = tc::smem_desc_sw128(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+        tc::mma_ss(tm, d, d, idesc, k != 0 ? 1u : 0u);
+      }
+      tc::mma_commit(mma_bar);
+    }
+    __syncwarp();
+  }
+  // row norms of k and q (the swizzle only permutes 16-byte pieces inside a 128-byte row, so a row sum needs no decode)
   if (a.flags & AVE_GDN_FLAG_QK_L2NORM) {
     const int i = tid >> 2, part = tid & 3;
     float sk = 0.f, sq = 0.f;
-    for (int d = part; d < D; d += 4) { const float kv = Ks[i * LDK + d], qv = Qs[i * LDK + d]; sk += kv * kv; sq += qv * qv; }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint4 kr = *reinterpret_cast<const uint4*>(smem + PP_KQ + half * 16384 + i * 128 + part * 32);
+      const uint4 kr2 = *reinterpret_cast<const uint4*>(smem + PP_KQ + half * 16384 + i * 128 + part * 32 + 16);
+      const uint4 qr = *reinterpret_cast<const uint4*>(smem + PP_KQ + 8192 + half * 16384 + i * 128 + part * 32);
+      const uint4 qr2 = *reinterpret_cast<const uint4*>(smem + PP_KQ + 8192 + half * 16384 + i * 128 + part * 32 + 16);
+      const uint32_t kw[8] = {kr.x, kr.y, kr.z, kr.w, kr2.x, kr2.y, kr2.z, kr2.w};
+      const uint32_t qw[8] = {qr.x, qr.y, qr.z, qr.w, qr2.x, qr2.y, qr2.z, qr2.w};
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float k0 = __uint_as_float(kw[w] << 16), k1 = __uint_as_float(kw[w] & 0xffff0000u);
+        const float q0 = __uint_as_float(qw[w] << 16), q1 = __uint_as_float(qw[w] & 0xffff0000u);
+        sk += k0 * k0 + k1 * k1; sq += q0 * q0 + q1 * q1;
+      }
+    }
     sk += __shfl_xor_sync(0xffffffffu, sk, 1); sk += __shfl_xor_sync(0xffffffffu, sk, 2);
     sq += __shfl_xor_sync(0xffffffffu, sq, 1); sq += __shfl_xor_sync(0xffffffffu, sq, 2);
     if (part == 0) { kn[i] = rsqrtf(sk + 1e-6f); qn[i] = rsqrtf(sq + 1e-6f); }
@@ -147,31 +180,72 @@ __global__ void __launch_bounds__(256) chunk_prep_kernel(const AveGdnArgs a, con
     sc[C + tid] = __expf(bC - bs[tid]) * kn[tid];    // Vd_j = ks_j Vn_j
     sc[2 * C + tid] = __expf(bC);
   }
-  // A (normalised k) -> shared;  P (normalised q, k) -> bf16 hi/lo
-  gram64(Ks, Ks, LDK, [&](int i, int j, float acc) {
-    As[i * (C + 1) + j] = (i > j) ? betas[i] * __expf(bs[i] - bs[j]) * acc * kn[i] * kn[j] : 0.f;
-  });
+  ok = ok && tc::mbar_wait(mma_bar, 0, abort_flag);
+  tc::tc_fence_after_sync();
   {
-    __nv_bfloat16* ph = out.p_hi + rec * (C * C);
-    __nv_bfloat16* pl = out.p_lo + rec * (C * C);
-    gram64(Qs, Ks, LDK, [&](int i, int j, float acc) {
-      const float p = (i >= j) ? __expf(bs[i] - bs[j]) * acc * qn[i] * kn[j] : 0.f;
-      __nv_bfloat16 hi, lo;
-      split_bf16(p, hi, lo);
-      ph[i * C + j] = hi; pl[i * C + j] = lo;
-    });
+    const int quarter = warp & 3, colhalf = warp >> 2;
+    const int r = quarter * 32 + lane;
+    uint32_t acc[32];
+    tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
+    tc::tmem_ld_wait();
+    if (r < C) {  // A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j)
+      const int i = r;
+      const float bi = bs[i], fi = betas[i] * kn[i];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        const int j = 32 * colhalf + jj;
+        As[i * (C + 1) + j] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[jj]) : 0.f;
+      }
+    } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
+      const int i = r - C;
+      const float bi = bs[i], fi = (i < cr.len) ? qn[i] : 0.f;
+      uint32_t ph[16], pl[16];
+#pragma unroll
+      for (int w = 0; w < 16; ++w) {
+        const int j = 32 * colhalf + 2 * w;
+        const float p0 = (i >= j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[2 * w]) : 0.f;
+        const float p1 = (i >= j + 1) ? fi * kn[j + 1] * __expf(bi - bs[j + 1]) * __uint_as_float(acc[2 * w + 1]) : 0.f;
+        ph[w] = pack_bf16x2(p0, p1);
+        pl[w] = pack_bf16x2(p0 - __uint_as_float(ph[w] << 16), p1 - __uint_as_float(ph[w] & 0xffff0000u));
+      }
+      uint4* dh = reinterpret_cast<uint4*>(out.p_hi + rec * (C * C) + i * C + 32 * colhalf);
+      uint4* dl = reinterpret_cast<uint4*>(out.p_lo + rec * (C * C) + i * C + 32 * colhalf);
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        dh[v4] = make_uint4(ph[4 * v4], ph[4 * v4 + 1], ph[4 * v4 + 2], ph[4 * v4 + 3]);
+        dl[v4] = make_uint4(pl[4 * v4], pl[4 * v4 + 1], pl[4 * v4 + 2], pl[4 * v4 + 3]);
+      }
+    }
   }
+  tc::tc_fence_before_sync();
   __syncthreads();
+  if (warp == 0) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tm, 64);
+  }
+  if (!ok) {
+    if (tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
+    return;
+  }
   // forward substitution, one column of [W | U] per thread
   {
     const int col = tid;
     const bool is_w = col < D;
+    const int cc = col & (D - 1);
+    // element (i, cc) of the swizzled K tile / of the plain V tile
+    const uint8_t* kcol = smem + PP_KQ + (cc >> 6) * 16384 + (cc & 7) * 2;
+    const int kchunk = (cc & 63) >> 3;
+    const __nv_bfloat16* vcol = reinterpret_cast<const __nv_bfloat16*>(smem + PP_V) + cc;
     float x[C];
 #pragma unroll
     for (int i = 0; i < C; ++i) {
       float rhs;
-      if (is_w) rhs = betas[i] * __expf(bs[i]) * kn[i] * Ks[i * LDK + col];
-      else rhs = (i < cr.len) ? betas[i] * bf2f(vg[(int64_t)(cr.t0 + i) * a.v_stride_t + (col - D)]) : 0.f;
+      if (is_w) {
+        const float kv = bf2f(*reinterpret_cast<const __nv_bfloat16*>(kcol + i * 128 + ((kchunk ^ (i & 7)) << 4)));
+        rhs = betas[i] * __expf(bs[i]) * kn[i] * kv;
+      } else {
+        rhs = betas[i] * bf2f(vcol[i * D]);
+      }
 #pragma unroll
       for (int j = 0; j < i; ++j) rhs = fmaf(-As[i * (C + 1) + j], x[j], rhs);
       x[i] = rhs;
@@ -182,7 +256,7 @@ __global__ void __launch_bounds__(256) chunk_prep_kernel(const AveGdnArgs a, con
 #pragma unroll
       for (int i = 0; i < C; ++i) { __nv_bfloat16 hi, lo; split_bf16(x[i], hi, lo); wh[i * D] = hi; wl[i * D] = lo; }
     } else {
-      float* u = out.u + rec * (C * D) + (col - D);
+      float* u = out.u + rec * (C * D) + cc;
 #pragma unroll
       for (int i = 0; i < C; ++i) u[i * D] = x[i];
     }
@@ -190,28 +264,44 @@ __global__ void __launch_bounds__(256) chunk_prep_kernel(const AveGdnArgs a, con
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
-constexpr int SCAN_THREADS = 320;
-constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728, ST_SCAL = 81920;
-constexpr int STAGE = 82944;                         // multiple of 1024
-constexpr uint32_t STAGE_TX = 4 * 16384 + 2 * 8192 + SCAL_FLOATS * 4;
-constexpr int OFF_STAGING = 2 * STAGE;               // fp32 [64][128]
-constexpr int OFF_BARS = OFF_STAGING + C * D * 4;
+constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA issuer; warpgroups 1,2: chain epilogue (two
+                                    // column groups); warpgroup 3: output.  Launch allocation is 128 registers per thread,
+                                    // redistributed below as 40 / 168 / 168 / 136 (sum 512).
+#ifndef AVE_REGS_CTRL
+#define AVE_REGS_CTRL 40
+#define AVE_REGS_CHAIN 168
+#define AVE_REGS_OUT 136
+#endif
+constexpr int REGS_CTRL = AVE_REGS_CTRL, REGS_CHAIN = AVE_REGS_CHAIN, REGS_OUT = AVE_REGS_OUT;
+static_assert(REGS_CTRL + 2 * REGS_CHAIN + REGS_OUT <= 4 * 128, "register redistribution exceeds the launch allocation");
+constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728;
+constexpr int STAGE = 81920;                         // multiple of 1024
+constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
+constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
+constexpr int OFF_SCAL = 2 * STAGE;                  // 2 x [qs | ks | decay]
+constexpr int OFF_U = OFF_SCAL + 2 * SCAL_BYTES;     // fp32 [64][128], single buffer
+constexpr int U_BYTES = C * D * 4;
+constexpr int OFF_STAGING = OFF_U + U_BYTES;         // fp32 [32][128]: half a chunk of output rows
+constexpr int OFF_BARS = OFF_STAGING + 32 * D * 4;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
 // TMEM columns
 constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO = 160, TM_VDHI = 192, TM_VDLO = 224,
                    TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
 
-struct ScanMaps {
-  CUtensorMap q, k, w_hi, w_lo, p_hi, p_lo;
-};
+#ifdef AVE_TRACE
+__device__ long long g_trace[16 * 1024];
+#define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot, c) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint32_t pack_hi(float x0, float x1) { return pack_bf16x2(x0, x1); }
 __device__ __forceinline__ uint32_t pack_lo(float x0, float x1, uint32_t hi_packed) {
   const float h0 = __uint_as_float(hi_packed << 16), h1 = __uint_as_float(hi_packed & 0xffff0000u);
   return pack_bf16x2(x0 - h0, x1 - h1);
 }
-// Barrier among the 8 epilogue warps built on an mbarrier so that, unlike bar.sync, the wait is bounded.
-__device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
+// Barrier among a group of warps built on an mbarrier so that, unlike bar.sync, the wait is bounded.
+__device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
   __syncwarp();
   if (lane == 0) tc::mbar_arrive(bar);
   const bool ok = tc::mbar_wait(bar, phase, abort_flag);
@@ -219,23 +309,41 @@ __device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, int lan
   return ok;
 }
 
+// Issues `ksteps` MMAs D (+)= A[tmem] * B[smem] over consecutive 16-wide K steps.  A advances 8 TMEM columns per
+// step; B advances b_step bytes per step and jumps b_half extra after four steps (second 64-wide K half of a
+// K-major tile; 0 when there is none).
+__device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, uint32_t b_step, uint32_t b_half,
+                                         uint32_t lbo, uint32_t idesc, int ksteps, bool accumulate) {
+  uint64_t desc = tc::smem_desc_sw128(b_smem, lbo, 1024);
+#pragma unroll 1
+  for (int k = 0; k < ksteps; ++k) {
+    tc::mma_ts(d_tmem, a_tmem, desc, idesc, (accumulate || k != 0) ? 1u : 0u);
+    a_tmem += 8;
+    desc += (uint64_t)((b_step + ((k == 3) ? b_half : 0u)) >> 4);
+  }
+}
+
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
-chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, const int32_t* __restrict__ chunk_start,
+chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
                      const float* __restrict__ u_ws, const float* __restrict__ scal_ws) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const float* u_s = reinterpret_cast<const float*>(smem + OFF_U);
   float* staging = reinterpret_cast<float*>(smem + OFF_STAGING);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
-  uint64_t* full = bars;          // [2]
-  uint64_t* empty = bars + 2;     // [2]
-  uint64_t* h_ready = bars + 4;
-  uint64_t* vn_full = bars + 5;
-  uint64_t* vn_ready = bars + 6;
-  uint64_t* dh_full = bars + 7;
-  uint64_t* o_full = bars + 8;
-  uint64_t* o_empty = bars + 9;
-  uint64_t* epi_bar = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* full = bars;          // [2] stage landed
+  uint64_t* empty = bars + 2;     // [2] stage consumed
+  uint64_t* h_ready = bars + 4;   // bf16 image of the state is in TMEM
+  uint64_t* vn_full = bars + 5;   // -(H W^T) accumulated
+  uint64_t* vn_ready = bars + 6;  // Vn / Vd hi+lo written back to TMEM
+  uint64_t* dh_full = bars + 7;   // state increment accumulated
+  uint64_t* o_full = bars + 8;    // both output accumulators complete
+  uint64_t* o_empty = bars + 9;   // output accumulators drained
+  uint64_t* u_full = bars + 10;
+  uint64_t* u_empty = bars + 11;
+  uint64_t* chain_bar = bars + 12;
+  uint64_t* out_bar = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -245,11 +353,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
   if (!sp.ok || sp.len == 0) {
     // zero-length sequence: the final state is the initial state
     if (sp.ok && a.final_state != nullptr && a.final_state != a.initial_state) {
-      int slot = a.state_indices ? a.state_indices[n] : n;
-      if (slot >= 0 && slot < a.num_slots) {
-        const int64_t tile = ((int64_t)slot * a.Hv + h) * (int64_t)(D * D);
+      const int slot0 = a.state_indices ? a.state_indices[n] : n;
+      if (slot0 >= 0 && slot0 < a.num_slots) {
+        const int64_t tile0 = ((int64_t)slot0 * a.Hv + h) * (int64_t)(D * D);
         for (int e = threadIdx.x; e < D * D; e += SCAN_THREADS)
-          a.final_state[tile + e] = a.initial_state ? a.initial_state[tile + e] : 0.f;
+          a.final_state[tile0 + e] = a.initial_state ? a.initial_state[tile0 + e] : 0.f;
       }
     }
     return;
@@ -273,10 +381,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&full[0], 1); tc::mbar_init(&full[1], 1);
-    tc::mbar_init(&empty[0], 9); tc::mbar_init(&empty[1], 9);
+    tc::mbar_init(&empty[0], 13); tc::mbar_init(&empty[1], 13);
     tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
-    tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 8);
-    tc::mbar_init(epi_bar, 8);
+    tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
+    tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 8);
+    tc::mbar_init(chain_bar, 8); tc::mbar_init(out_bar, 4);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -286,6 +395,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
 
+  if (warp < 4) {
+  tc::reg_set<REGS_CTRL, 128>();
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
     if (lane == 0) {
@@ -308,77 +419,75 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
         tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
         tc::tma_load_2d(st + ST_PHI, &maps.p_hi, &full[s], 0, row);
         tc::tma_load_2d(st + ST_PLO, &maps.p_lo, &full[s], 0, row);
-        tc::bulk_load(st + ST_SCAL, scal_ws + rec * SCAL_FLOATS, SCAL_FLOATS * 4, &full[s]);
+        tc::bulk_load(smem + OFF_SCAL + s * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
+        // U of chunk c replaces U of chunk c-1 once the chain epilogue has consumed it
+        if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
+        tc::mbar_expect_tx(u_full, U_BYTES);
+        tc::bulk_load(smem + OFF_U, u_ws + rec * (C * D), U_BYTES, u_full);
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, false, true, false);   // negated A
-      constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
-      constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
-      for (int c = 0; c < n_chunks; ++c) {
-        const int s = c & 1;
-        const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-        const uint32_t sb = tc::smem_u32(smem + s * STAGE);
-        if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) break;
-        if (!tc::mbar_wait(h_ready, cp, abort_flag)) break;
-        tc::tc_fence_after_sync();
-        // Vn^T accumulator = -(Hhi Whi^T + Hlo Whi^T + Hhi Wlo^T)
-#pragma unroll
-        for (int t = 0; t < 3; ++t) {
-          const uint32_t a_col = (t == 1) ? TM_HLO : TM_HHI;
-          const uint32_t b_base = sb + ((t == 2) ? ST_WLO : ST_WHI);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            tc::mma_ts(tm + TM_VN, tm + a_col + 8 * k, tc::smem_desc_sw128(b_base + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), id_vn,
-                       (t | k) != 0 ? 1u : 0u);
-        }
+    // ------------------------------------------------------------------ MMA issuer (whole warp runs the loop,
+    // one elected lane issues)
+    constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, false, true, false);   // negated A
+    constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
+    constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
+    for (int c = 0; c < n_chunks; ++c) {
+      const int s = c & 1;
+      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
+      const uint32_t sb = tc::smem_u32(smem + s * STAGE);
+      if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) break;
+      TRACE(0, c);
+      if (!tc::mbar_wait(h_ready, cp, abort_flag)) break;
+      TRACE(1, c);
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
+        // Vn^T accumulator = -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); a K-major tile is two 64-wide halves 8 KB apart
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 32, 8192 - 128, 16, id_vn, 8, false);
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 32, 8192 - 128, 16, id_vn, 8, true);
+        issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 32, 8192 - 128, 16, id_vn, 8, true);
         tc::mma_commit(vn_full);
-        if (!tc::mbar_wait(o_empty, cp ^ 1u, abort_flag)) break;
-        tc::tc_fence_after_sync();
+      }
+      __syncwarp();
+      TRACE(2, c);
+      if (!tc::mbar_wait(o_empty, cp ^ 1u, abort_flag)) break;
+      TRACE(3, c);
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
         // O1 = (Hhi + Hlo) Q^T
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            tc::mma_ts(tm + TM_O1, tm + (t ? TM_HLO : TM_HHI) + 8 * k,
-                       tc::smem_desc_sw128(sb + ST_Q + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), id_n64, (t | k) != 0 ? 1u : 0u);
-        }
-        if (!tc::mbar_wait(vn_ready, cp, abort_flag)) break;
-        tc::tc_fence_after_sync();
-        // dH = (Vd_hi + Vd_lo)^T-contracted with K over the chunk's tokens
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc::mma_ts(tm + TM_DH, tm + (t ? TM_VDLO : TM_VDHI) + 8 * k, tc::smem_desc_sw128(sb + ST_K + k * 2048, 8192, 1024), id_dh,
-                       (t | k) != 0 ? 1u : 0u);
-        }
+        issue_ts(tm + TM_O1, tm + TM_HHI, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, false);
+        issue_ts(tm + TM_O1, tm + TM_HLO, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, true);
+      }
+      __syncwarp();
+      if (!tc::mbar_wait(vn_ready, cp, abort_flag)) break;
+      TRACE(4, c);
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
+        // dH = (Vd_hi + Vd_lo) contracted with K over the chunk's tokens (K tile read MN-major: 16 token rows per step)
+        issue_ts(tm + TM_DH, tm + TM_VDHI, sb + ST_K, 2048, 0, 8192, id_dh, 4, false);
+        issue_ts(tm + TM_DH, tm + TM_VDLO, sb + ST_K, 2048, 0, 8192, id_dh, 4, true);
         tc::mma_commit(dh_full);
         // O2 = Vn_hi Phi^T + Vn_lo Phi^T + Vn_hi Plo^T
-#pragma unroll
-        for (int t = 0; t < 3; ++t) {
-          const uint32_t a_col = (t == 1) ? TM_VNLO : TM_VNHI;
-          const uint32_t b_base = sb + ((t == 2) ? ST_PLO : ST_PHI);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc::mma_ts(tm + TM_O2, tm + a_col + 8 * k, tc::smem_desc_sw128(b_base + k * 32, 16, 1024), id_n64, (t | k) != 0 ? 1u : 0u);
-        }
+        issue_ts(tm + TM_O2, tm + TM_VNHI, sb + ST_PHI, 32, 0, 16, id_n64, 4, false);
+        issue_ts(tm + TM_O2, tm + TM_VNLO, sb + ST_PHI, 32, 0, 16, id_n64, 4, true);
+        issue_ts(tm + TM_O2, tm + TM_VNHI, sb + ST_PLO, 32, 0, 16, id_n64, 4, true);
         tc::mma_commit(o_full);
         tc::mma_commit(&empty[s]);
       }
+      __syncwarp();
+      TRACE(5, c);
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue groups
-    const int ew = warp - 2;            // 0..7
-    const int grp = ew >> 2;            // column half
+  }
+  } else if (warp < 12) {
+    tc::reg_set<REGS_CHAIN, 128>();
+    // ------------------------------------------------------------------ chain epilogue: Vn/Vd conversion and state update
+    const int grp = (warp - 4) >> 2;    // column half
     const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
     const int d = quarter * 32 + lane;  // row of H (d_v index)
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
     const int64_t tile = ((int64_t)slot * a.Hv + h) * (int64_t)(D * D);
     bool alive = true;
-    uint32_t epi_phase = 0;
+    uint32_t sync_phase = 0;
 
     float Hreg[64];  // H[d][64*grp + i] = M[64*grp + i][d]
     if (a.initial_state != nullptr) {
@@ -389,14 +498,17 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
       for (int i = 0; i < 64; ++i) Hreg[i] = 0.f;
     }
     auto publish_h = [&]() {
-      uint32_t hi[32], lo[32];
 #pragma unroll
-      for (int w = 0; w < 32; ++w) {
-        hi[w] = pack_hi(Hreg[2 * w], Hreg[2 * w + 1]);
-        lo[w] = pack_lo(Hreg[2 * w], Hreg[2 * w + 1], hi[w]);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int w = 0; w < 16; ++w) {
+          hi[w] = pack_hi(Hreg[32 * half + 2 * w], Hreg[32 * half + 2 * w + 1]);
+          lo[w] = pack_lo(Hreg[32 * half + 2 * w], Hreg[32 * half + 2 * w + 1], hi[w]);
+        }
+        tc::tmem_st16(lane_addr + TM_HHI + 32 * grp + 16 * half, hi);
+        tc::tmem_st16(lane_addr + TM_HLO + 32 * grp + 16 * half, lo);
       }
-      tc::tmem_st32(lane_addr + TM_HHI + 32 * grp, hi);
-      tc::tmem_st32(lane_addr + TM_HLO + 32 * grp, lo);
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
       __syncwarp();
@@ -407,47 +519,53 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
     for (int c = 0; c < n_chunks && alive; ++c) {
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-      const int64_t rec = (int64_t)(c_first + c) * a.Hv + h;
-      const float* scal = reinterpret_cast<const float*>(smem + s * STAGE + ST_SCAL);
-      const int len = min(C, sp.len - c * C);
-      // U^T for this thread's row and token half, fetched before the accumulator is ready
-      float uv[32];
-      {
-        const float* up = u_ws + rec * (C * D) + (int64_t)(32 * grp) * D + d;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) uv[j] = __ldg(up + j * D);
-      }
+      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + s * SCAL_BYTES);
       if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait(u_full, cp, abort_flag)) { alive = false; break; }
+      if (warp == 4 && lane == 0) TRACE(6, c);
       if (!tc::mbar_wait(vn_full, cp, abort_flag)) { alive = false; break; }
+      if (warp == 4 && lane == 0) TRACE(7, c);
       tc::tc_fence_after_sync();
       {
         uint32_t acc[32];
         tc::tmem_ld32(lane_addr + TM_VN + 32 * grp, acc);
-        tc::tmem_ld_wait();
-        // both groups have read the accumulator before its columns are reused
-        if (!epi_sync(epi_bar, epi_phase, lane, abort_flag)) { alive = false; break; }
-        uint32_t vh[16], vl[16], dh[16], dl[16];
+        float v[32];
 #pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          const float v0 = uv[2 * w] + __uint_as_float(acc[2 * w]);
-          const float v1 = uv[2 * w + 1] + __uint_as_float(acc[2 * w + 1]);
-          vh[w] = pack_hi(v0, v1);
-          vl[w] = pack_lo(v0, v1, vh[w]);
-          const float e0 = v0 * scal[C + 32 * grp + 2 * w], e1 = v1 * scal[C + 32 * grp + 2 * w + 1];
-          dh[w] = pack_hi(e0, e1);
-          dl[w] = pack_lo(e0, e1, dh[w]);
+        for (int j = 0; j < 32; ++j) v[j] = u_s[(32 * grp + j) * D + d];
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(acc[j]);
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(u_empty);
+        // both groups have read the accumulator before its columns are reused
+        if (!group_sync(chain_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
+        {
+          uint32_t vh[16], vl[16];
+#pragma unroll
+          for (int w = 0; w < 16; ++w) { vh[w] = pack_hi(v[2 * w], v[2 * w + 1]); vl[w] = pack_lo(v[2 * w], v[2 * w + 1], vh[w]); }
+          tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
+          tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
         }
-        tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
-        tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
-        tc::tmem_st16(lane_addr + TM_VDHI + 16 * grp, dh);
-        tc::tmem_st16(lane_addr + TM_VDLO + 16 * grp, dl);
+        {
+          uint32_t dh[16], dl[16];
+#pragma unroll
+          for (int w = 0; w < 16; ++w) {
+            const float2 ks = *reinterpret_cast<const float2*>(scal + C + 32 * grp + 2 * w);
+            const float e0 = v[2 * w] * ks.x, e1 = v[2 * w + 1] * ks.y;
+            dh[w] = pack_hi(e0, e1);
+            dl[w] = pack_lo(e0, e1, dh[w]);
+          }
+          tc::tmem_st16(lane_addr + TM_VDHI + 16 * grp, dh);
+          tc::tmem_st16(lane_addr + TM_VDLO + 16 * grp, dl);
+        }
         tc::tmem_st_wait();
         tc::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(vn_ready);
       }
-      // state update
+      if (warp == 4 && lane == 0) TRACE(8, c);
       if (!tc::mbar_wait(dh_full, cp, abort_flag)) { alive = false; break; }
+      if (warp == 4 && lane == 0) TRACE(9, c);
       tc::tc_fence_after_sync();
       {
         const float decay = scal[2 * C];
@@ -461,59 +579,123 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ ScanMaps maps, 
         }
         publish_h();
       }
-      // output
-      if (!tc::mbar_wait(o_full, cp, abort_flag)) { alive = false; break; }
-      tc::tc_fence_after_sync();
-      {
-        uint32_t o1[32], o2[32];
-        tc::tmem_ld32(lane_addr + TM_O1 + 32 * grp, o1);
-        tc::tmem_ld32(lane_addr + TM_O2 + 32 * grp, o2);
-        tc::tmem_ld_wait();
-        tc::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(o_empty);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int i = 32 * grp + j;
-          staging[i * D + d] = a.scale * fmaf(scal[i], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
-        }
-      }
-      if (!epi_sync(epi_bar, epi_phase, lane, abort_flag)) { alive = false; break; }
-      {
-        const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
-#pragma unroll 1
-        for (int r = 0; r < 8; ++r) {
-          const int i = ew * 8 + r;
-          if (i >= len) break;
-          const int64_t tok = sp.t0 + c * C + i;
-          float4 ov = *reinterpret_cast<const float4*>(staging + i * D + 4 * lane);
-          float o4[4] = {ov.x, ov.y, ov.z, ov.w};
-          if (a.z != nullptr) {
-            float zz[4];
-            unpack_bf16x4(*reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b +
-                                                          tok * a.z_stride_t + (int64_t)h * a.z_stride_h + 4 * lane), zz);
-            if (gate_first) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) o4[e] *= silu(zz[e]);
-            }
-            const float ss = warp_sum(o4[0] * o4[0] + o4[1] * o4[1] + o4[2] * o4[2] + o4[3] * o4[3]);
-            const float rinv = rsqrtf(ss * (1.0f / D) + a.norm_eps);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float w = a.norm_weight ? a.norm_weight[4 * lane + e] : 1.0f;
-              o4[e] = o4[e] * rinv * w * (gate_first ? 1.0f : silu(zz[e]));
-            }
-          }
-          *reinterpret_cast<uint2*>(og + tok * a.o_stride_t + 4 * lane) = make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3]));
-        }
-      }
-      // staging may be overwritten by the next chunk
-      if (!epi_sync(epi_bar, epi_phase, lane, abort_flag)) { alive = false; break; }
-      if (lane == 0) tc::mbar_arrive(&empty[s]);
+      if (lane == 0) tc::mbar_arrive(&empty[s]);  // this warp no longer reads the stage's scale vectors
+      if (warp == 4 && lane == 0) TRACE(10, c);
     }
     if (alive && a.final_state != nullptr) {
 #pragma unroll
       for (int i = 0; i < 64; ++i) a.final_state[tile + (int64_t)(64 * grp + i) * D + d] = Hreg[i];
+    }
+  } else {
+    tc::reg_set<REGS_OUT, 128>();
+    // ------------------------------------------------------------------ output warps: o = scale (qs_i O1 + O2), gated norm, store
+    const int ow = warp - 12;           // 0..3
+    const int quarter = warp & 3;
+    const int d = quarter * 32 + lane;
+    const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
+    const __nv_bfloat16* zg = a.z ? reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (int64_t)h * a.z_stride_h + 4 * lane
+                                  : nullptr;
+    const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
+    float nw[4] = {1.f, 1.f, 1.f, 1.f};
+    if (a.norm_weight != nullptr) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) nw[e] = a.norm_weight[4 * lane + e];
+    }
+    uint32_t sync_phase = 0;
+    bool alive = true;
+    for (int c = 0; c < n_chunks && alive; ++c) {
+      const int s = c & 1;
+      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
+      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + s * SCAL_BYTES);
+      const int len = min(C, sp.len - c * C);
+      // gate rows of this warp's output tokens (8 per half chunk), issued before the accumulators are complete
+      uint2 zraw[2][8];
+      if (zg != nullptr) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int i = 32 * half + ow * 8 + r;
+            zraw[half][r] = (i < len) ? *reinterpret_cast<const uint2*>(zg + (int64_t)(sp.t0 + c * C + i) * a.z_stride_t) : make_uint2(0u, 0u);
+          }
+      }
+      if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait(o_full, cp, abort_flag)) { alive = false; break; }
+      if (warp == 12 && lane == 0) TRACE(11, c);
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        // this thread's row d, tokens [32 half, 32 half + 32)
+#pragma unroll
+        for (int q4 = 0; q4 < 2; ++q4) {
+          uint32_t o1[16], o2[16];
+          tc::tmem_ld16(lane_addr + TM_O1 + 32 * half + 16 * q4, o1);
+          tc::tmem_ld16(lane_addr + TM_O2 + 32 * half + 16 * q4, o2);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * half + 16 * q4 + 4 * j4);
+            const float qv[4] = {qs.x, qs.y, qs.z, qs.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = 4 * j4 + e;
+              staging[(16 * q4 + j) * D + d] = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
+            }
+          }
+        }
+        if (half == 1) {  // both accumulators fully drained
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(o_empty);
+        }
+        if (half == 0 && warp == 12 && lane == 0) TRACE(13, c);
+        if (!group_sync(out_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
+        if (half == 0 && warp == 12 && lane == 0) TRACE(14, c);
+        {
+          float o4[8][4], gz[8][4], ss[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float4 ov = *reinterpret_cast<const float4*>(staging + (ow * 8 + r) * D + 4 * lane);
+            o4[r][0] = ov.x; o4[r][1] = ov.y; o4[r][2] = ov.z; o4[r][3] = ov.w;
+            if (zg != nullptr) {
+              float zz[4];
+              unpack_bf16x4(zraw[half][r], zz);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) gz[r][e] = silu(zz[e]);
+              if (gate_first) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { o4[r][e] *= gz[r][e]; gz[r][e] = 1.0f; }
+              }
+              ss[r] = o4[r][0] * o4[r][0] + o4[r][1] * o4[r][1] + o4[r][2] * o4[r][2] + o4[r][3] * o4[r][3];
+            }
+          }
+          if (zg != nullptr) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+              for (int r = 0; r < 8; ++r) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], off);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              const float rinv = rsqrtf(ss[r] * (1.0f / D) + a.norm_eps);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) o4[r][e] = o4[r][e] * rinv * nw[e] * gz[r][e];
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int i = 32 * half + ow * 8 + r;
+            if (i < len)
+              *reinterpret_cast<uint2*>(og + (int64_t)(sp.t0 + c * C + i) * a.o_stride_t + 4 * lane) =
+                  make_uint2(pack_bf16x2(o4[r][0], o4[r][1]), pack_bf16x2(o4[r][2], o4[r][3]));
+          }
+        }
+        if (half == 0 && warp == 12 && lane == 0) TRACE(15, c);
+        // staging may be overwritten by the next half
+        if (!group_sync(out_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
+      }
+      if (lane == 0) tc::mbar_arrive(&empty[s]);
+      if (warp == 12 && lane == 0) TRACE(12, c);
     }
   }
 
@@ -552,6 +734,12 @@ WsLayout ws_layout(const AveGdnArgs& a) {
 
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
 
+#ifdef AVE_TRACE
+extern "C" int ave_trace_read(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
+}
+#endif
+
 int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
   const WsLayout L = ws_layout(a);
   if (L.chunks == 0 || a.n_seqs == 0) return AVE_GDN_OK;
@@ -565,7 +753,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
   po.u = reinterpret_cast<float*>(ws + L.u);
   po.scal = reinterpret_cast<float*>(ws + L.scal);
 
-  ScanMaps maps;
+  GdnMaps maps;
   const uint64_t rows = (uint64_t)L.chunks * a.Hv * C;
   {
     const uint64_t dw[2] = {D, rows}, sw[2] = {2, D * 2}, dp[2] = {C, rows}, spp[2] = {2, C * 2};
@@ -581,10 +769,14 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
     const uint64_t sk[4] = {2, (uint64_t)a.k_stride_h * 2, (uint64_t)a.k_stride_t * 2, (uint64_t)(a.B > 1 ? a.k_stride_b : a.k_stride_t * a.T) * 2};
     if ((rc = make_tmap(&maps.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.q), 4, dq, sq, box4, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.k), 4, dq, sk, box4, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    const uint32_t boxv[4] = {D, 1, 64, 1};
+    const uint64_t dv4[4] = {D, (uint64_t)a.Hv, (uint64_t)a.T, (uint64_t)a.B};
+    const uint64_t sv[4] = {2, (uint64_t)a.v_stride_h * 2, (uint64_t)a.v_stride_t * 2, (uint64_t)(a.B > 1 ? a.v_stride_b : a.v_stride_t * a.T) * 2};
+    if ((rc = make_tmap(&maps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.v), 4, dv4, sv, boxv, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
   }
 
   if (a.cu_seqlens != nullptr) chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start);
-  constexpr size_t smem_prep = sizeof(float) * (2 * C * (D + 1) + C * (C + 1) + 4 * C);
+  constexpr size_t smem_prep = PREP_SMEM;
   static bool attr_set_dev[64] = {};
   int dev = 0;
   AVE_CUDA_TRY(cudaGetDevice(&dev));
@@ -593,7 +785,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
     attr_set_dev[dev & 63] = true;
   }
-  chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), 256, smem_prep, stream>>>(a, chunk_start, po);
+  chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po);
   AVE_CUDA_TRY(cudaGetLastError());
   chunk_scan_tc_kernel<<<(unsigned)a.n_seqs * (unsigned)a.Hv, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal);
   AVE_CUDA_TRY(cudaGetLastError());

@@ -37,10 +37,32 @@ constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef AVE_SPIN_SLEEP
+    __nanosleep(AVE_SPIN_SLEEP);
+#endif
     if ((it & 63u) == 63u && *abort_flag != 0u) return false;
   }
   *abort_flag = 1u;
   return false;
+}
+
+// One lane of a converged warp; the enclosing control flow stays warp-uniform, which lets the compiler keep
+// descriptors in uniform registers for the MMA issue.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
+}
+
+// Per-warpgroup register budget (all four warps of an aligned warpgroup execute it together).  The sum over the
+// CTA's warpgroups must stay within the kernel's launch-time allocation or the increase never completes.
+// A decrease to more, or an increase to fewer, registers than the warp currently owns is an illegal instruction,
+// so the direction is derived from the launch-time count.
+template <int N, int LAUNCH_REGS>
+__device__ __forceinline__ void reg_set() {
+  static_assert(N % 8 == 0 && N >= 24 && N <= 256, "register count must be a multiple of 8 in [24, 256]");
+  if constexpr (N > LAUNCH_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+  else if constexpr (N < LAUNCH_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------- proxies / fences
