@@ -1,0 +1,127 @@
+"""Qwen3-Next gated-delta-net block, sharded by heads across the GPUs of one node.
+
+Order of operations: bf16 in-projection (this rank's columns only) -> depthwise causal conv1d (kernel 4) + SiLU on
+q/k/v -> q/k L2 norm (inside the delta-rule kernel) -> gate/beta -> chunked delta rule on this rank's heads ->
+gated RMSNorm (fused into the delta-rule epilogue) -> all-gather of the per-head outputs over NCCL.
+
+Partitioning: rank r of G owns key heads [r*Hk/G, (r+1)*Hk/G) and the value heads that read them.  Every
+(sequence, value head) recurrence is independent, so nothing crosses GPUs before the final all-gather; the
+in-projection weight is sliced by output column so that each rank produces exactly its own heads.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass(frozen=True)
+class HeadShard:
+    """Head ranges of one rank."""
+    rank: int
+    world: int
+    Hk: int
+    Hv: int
+
+    def __post_init__(self):
+        if self.Hk % self.world or self.Hv % self.Hk:
+            raise ValueError(f"key heads ({self.Hk}) must divide by the world size ({self.world}) and value heads "
+                             f"({self.Hv}) by key heads")
+
+    @property
+    def key_heads(self) -> range:
+        n = self.Hk // self.world
+        return range(self.rank * n, (self.rank + 1) * n)
+
+    @property
+    def value_heads(self) -> range:
+        n = self.Hv // self.world
+        return range(self.rank * n, (self.rank + 1) * n)
+
+
+def projection_rows(shard: HeadShard, dk: int, dv: int) -> torch.Tensor:
+    """Row indices of the fused in-projection weight [q | k | v | z | b | a] (rows = output features) that produce
+    this rank's heads, in the order q, k, v, z, b, a."""
+    Hk, Hv = shard.Hk, shard.Hv
+    off_q, off_k, off_v = 0, Hk * dk, 2 * Hk * dk
+    off_z, off_b, off_a = off_v + Hv * dv, off_v + 2 * Hv * dv, off_v + 2 * Hv * dv + Hv
+    kh, vh = shard.key_heads, shard.value_heads
+    parts = [torch.arange(off_q + kh.start * dk, off_q + kh.stop * dk),
+             torch.arange(off_k + kh.start * dk, off_k + kh.stop * dk),
+             torch.arange(off_v + vh.start * dv, off_v + vh.stop * dv),
+             torch.arange(off_z + vh.start * dv, off_z + vh.stop * dv),
+             torch.arange(off_b + vh.start, off_b + vh.stop),
+             torch.arange(off_a + vh.start, off_a + vh.stop)]
+    return torch.cat(parts)
+
+
+def pad_rows(n: int, multiple: int = 8) -> int:
+    return (n + multiple - 1) // multiple * multiple
+
+
+class GdnBlockShard:
+    """One rank's slice of the block.  ``w_in`` is the full fused projection weight ``[2*Hk*dk + 2*Hv*dv + 2*Hv, hidden]``;
+    ``conv_w`` the full depthwise filter ``[2*Hk*dk + Hv*dv, 4]``; ``A_log``, ``dt_bias``, ``norm_weight`` per value head /
+    per feature.  Only this rank's rows are kept on the device."""
+
+    def __init__(self, w_in, conv_w, A_log, dt_bias, norm_weight, *, Hk, Hv, dk, dv, rank=0, world=1, device="cuda"):
+        self.shard = HeadShard(rank, world, Hk, Hv)
+        self.Hk, self.Hv, self.dk, self.dv = Hk, Hv, dk, dv
+        self.hk_local, self.hv_local = Hk // world, Hv // world
+        rows = projection_rows(self.shard, dk, dv)
+        self.n_rows = rows.numel()
+        w = w_in[rows].to(torch.bfloat16)
+        pad = pad_rows(self.n_rows) - self.n_rows
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype)], 0)
+        self.w = w.to(device).contiguous()
+        nq, nk, nv = self.hk_local * dk, self.hk_local * dk, self.hv_local * dv
+        self.splits = (nq, nk, nv, nv, self.hv_local, self.hv_local)
+        conv_rows = rows[: nq + nk + nv].clone()
+        # conv filter rows follow the q | k | v feature order of the projection
+        self.conv_w = conv_w[conv_rows].to(torch.bfloat16).to(device).contiguous()
+        vh = self.shard.value_heads
+        self.A_log = A_log[vh.start:vh.stop].float().to(device).contiguous()
+        self.dt_bias = dt_bias[vh.start:vh.stop].float().to(device).contiguous()
+        self.norm_weight = None if norm_weight is None else norm_weight.float().to(device).contiguous()
+
+    def forward_local(self, x: torch.Tensor, cu_seqlens=None) -> torch.Tensor:
+        """x: bf16 [B, T, hidden] (replicated on every rank).  Returns this rank's normalised head outputs
+        [B, T, Hv/G, dv]."""
+        from . import gdn, gemm
+        B, T, hidden = x.shape
+        y2 = gemm.gemm_pipeline_transposed_b(x.reshape(B * T, hidden), self.w)
+        y = y2.reshape(B, T, -1)
+        nq, nk, nv, nz, nb, na = self.splits
+        qkv_in = y[:, :, : nq + nk + nv]
+        z = y[:, :, nq + nk + nv: nq + nk + nv + nz].reshape(B, T, self.hv_local, self.dv)
+        o0 = nq + nk + nv + nz
+        b_in, a_in = y2[:, o0: o0 + nb], y2[:, o0 + nb: o0 + nb + na]
+        qkv = gdn.causal_conv1d_silu(qkv_in, self.conv_w, cu_seqlens=cu_seqlens)
+        q = qkv[:, :, :nq].reshape(B, T, self.hk_local, self.dk)
+        k = qkv[:, :, nq: nq + nk].reshape(B, T, self.hk_local, self.dk)
+        v = qkv[:, :, nq + nk:].reshape(B, T, self.hv_local, self.dv)
+        g, beta = gdn.gate_beta(a_in, b_in, self.A_log, self.dt_bias)
+        g, beta = g.reshape(B, T, self.hv_local), beta.reshape(B, T, self.hv_local)
+        o, _ = gdn.chunk_gated_delta_rule(q, k, v, g, beta, use_qk_l2norm_in_kernel=True, cu_seqlens=cu_seqlens,
+                                          z=z, norm_weight=self.norm_weight)
+        return o
+
+    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None) -> torch.Tensor:
+        """Full block output [B, T, Hv, dv] on every rank: local heads, then an all-gather over the head dimension."""
+        o = self.forward_local(x, cu_seqlens)
+        return gather_heads(o, self.shard.world, group)
+
+
+def gather_heads(o_local: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """All-gather of [B, T, Hv/G, dv] head slices into [B, T, Hv, dv] (rank-major gather, then one transpose copy)."""
+    if world == 1:
+        return o_local
+    import torch.distributed as dist
+    B, T, hl, dv = o_local.shape
+    buf = torch.empty((world, B, T, hl, dv), dtype=o_local.dtype, device=o_local.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(buf, o_local.contiguous(), group=group)
+    else:  # host-side backends (used by the CPU tests) only have the list form
+        dist.all_gather(list(buf.unbind(0)), o_local.contiguous(), group=group)
+    return buf.permute(1, 2, 0, 3, 4).reshape(B, T, world * hl, dv)

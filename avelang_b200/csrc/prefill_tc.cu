@@ -83,14 +83,14 @@ struct GdnMaps {
 // K, 64..127 = Q) and the K rows alone as its N = 64 B operand: lanes 0..63 of the accumulator are K K^T, lanes
 // 64..127 are Q K^T.
 constexpr int PREP_THREADS = 256;
-constexpr int PP_KQ = 0, PP_V = 32768, PP_A = 49152, PP_SC = PP_A + C * (C + 1) * 4, PP_BARS = PP_SC + 4 * C * 4;
+constexpr int PP_KQ = 0, PP_V = 32768, PP_A = 49152, PP_SC = PP_A + C * C * 4, PP_BARS = PP_SC + 4 * C * 4;
 constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
 
 __global__ void __launch_bounds__(PREP_THREADS, 2)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][65]
+  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][64], row i holds A[i][0..i-1]
   float* bs = reinterpret_cast<float*>(smem + PP_SC);
   float* betas = bs + C;
   float* qn = betas + C;
@@ -194,7 +194,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
         const int j = 32 * colhalf + jj;
-        As[i * (C + 1) + j] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[jj]) : 0.f;
+        As[i * C + j] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[jj]) : 0.f;
       }
     } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
       const int i = r - C;
@@ -246,9 +246,17 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       } else {
         rhs = betas[i] * bf2f(vcol[i * D]);
       }
+      // A[i][j] is zero for j >= i, so whole float4 groups can be consumed; two accumulators shorten the chain
+      float r2 = 0.f;
 #pragma unroll
-      for (int j = 0; j < i; ++j) rhs = fmaf(-As[i * (C + 1) + j], x[j], rhs);
-      x[i] = rhs;
+      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+        const float4 av = *reinterpret_cast<const float4*>(As + i * C + 4 * j4);
+        rhs = fmaf(-av.x, x[4 * j4], rhs);
+        if (4 * j4 + 1 < i) r2 = fmaf(-av.y, x[4 * j4 + 1], r2);
+        if (4 * j4 + 2 < i) rhs = fmaf(-av.z, x[4 * j4 + 2], rhs);
+        if (4 * j4 + 3 < i) r2 = fmaf(-av.w, x[4 * j4 + 3], r2);
+      }
+      x[i] = rhs + r2;
     }
     if (is_w) {
       __nv_bfloat16* wh = out.w_hi + rec * (C * D) + col;
@@ -266,10 +274,10 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 // ------------------------------------------------------------------------------------------------ pass 2
 constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA issuer; warpgroups 1,2: chain epilogue (two
                                     // column groups); warpgroup 3: output.  Launch allocation is 128 registers per thread,
-                                    // redistributed below as 40 / 168 / 168 / 136 (sum 512).
+                                    // redistributed below as 56 / 160 / 160 / 136 (sum 512).
 #ifndef AVE_REGS_CTRL
-#define AVE_REGS_CTRL 40
-#define AVE_REGS_CHAIN 168
+#define AVE_REGS_CTRL 56
+#define AVE_REGS_CHAIN 160
 #define AVE_REGS_OUT 136
 #endif
 constexpr int REGS_CTRL = AVE_REGS_CTRL, REGS_CHAIN = AVE_REGS_CHAIN, REGS_OUT = AVE_REGS_OUT;
@@ -314,12 +322,12 @@ __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int l
 // K-major tile; 0 when there is none).
 __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, uint32_t b_step, uint32_t b_half,
                                          uint32_t lbo, uint32_t idesc, int ksteps, bool accumulate) {
-  uint64_t desc = tc::smem_desc_sw128(b_smem, lbo, 1024);
-#pragma unroll 1
-  for (int k = 0; k < ksteps; ++k) {
-    tc::mma_ts(d_tmem, a_tmem, desc, idesc, (accumulate || k != 0) ? 1u : 0u);
-    a_tmem += 8;
-    desc += (uint64_t)((b_step + ((k == 3) ? b_half : 0u)) >> 4);
+  const uint64_t desc = tc::smem_desc_sw128(b_smem, lbo, 1024);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (k < ksteps)
+      tc::mma_ts(d_tmem, a_tmem + 8 * k, desc + (uint64_t)((k * b_step + ((k > 3) ? b_half : 0u)) >> 4), idesc,
+                 (accumulate || k != 0) ? 1u : 0u);
   }
 }
 
@@ -343,7 +351,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   uint64_t* u_empty = bars + 11;
   uint64_t* chain_bar = bars + 12;
   uint64_t* out_bar = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* vd_ready = bars + 14; // Vd hi+lo written to TMEM (the state update needs nothing else)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -385,7 +394,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
     tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
     tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 8);
-    tc::mbar_init(chain_bar, 8); tc::mbar_init(out_bar, 4);
+    tc::mbar_init(chain_bar, 8); tc::mbar_init(out_bar, 4); tc::mbar_init(vd_ready, 8);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -459,7 +468,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         issue_ts(tm + TM_O1, tm + TM_HLO, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, true);
       }
       __syncwarp();
-      if (!tc::mbar_wait(vn_ready, cp, abort_flag)) break;
+      if (!tc::mbar_wait(vd_ready, cp, abort_flag)) break;
       TRACE(4, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
@@ -467,6 +476,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         issue_ts(tm + TM_DH, tm + TM_VDHI, sb + ST_K, 2048, 0, 8192, id_dh, 4, false);
         issue_ts(tm + TM_DH, tm + TM_VDLO, sb + ST_K, 2048, 0, 8192, id_dh, 4, true);
         tc::mma_commit(dh_full);
+      }
+      __syncwarp();
+      if (!tc::mbar_wait(vn_ready, cp, abort_flag)) break;
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
         // O2 = Vn_hi Phi^T + Vn_lo Phi^T + Vn_hi Plo^T
         issue_ts(tm + TM_O2, tm + TM_VNHI, sb + ST_PHI, 32, 0, 16, id_n64, 4, false);
         issue_ts(tm + TM_O2, tm + TM_VNLO, sb + ST_PHI, 32, 0, 16, id_n64, 4, true);
@@ -537,16 +551,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(acc[j]);
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(u_empty);
-        // both groups have read the accumulator before its columns are reused
-        if (!group_sync(chain_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
-        {
-          uint32_t vh[16], vl[16];
-#pragma unroll
-          for (int w = 0; w < 16; ++w) { vh[w] = pack_hi(v[2 * w], v[2 * w + 1]); vl[w] = pack_lo(v[2 * w], v[2 * w + 1], vh[w]); }
-          tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
-          tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
-        }
-        {
+        {  // Vd first: its columns alias nothing, and the state update waits only for it
           uint32_t dh[16], dl[16];
 #pragma unroll
           for (int w = 0; w < 16; ++w) {
@@ -557,11 +562,24 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           }
           tc::tmem_st16(lane_addr + TM_VDHI + 16 * grp, dh);
           tc::tmem_st16(lane_addr + TM_VDLO + 16 * grp, dl);
+          tc::tmem_st_wait();
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(vd_ready);
         }
-        tc::tmem_st_wait();
-        tc::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(vn_ready);
+        // both groups have read the accumulator before its columns are reused for Vn hi/lo
+        if (!group_sync(chain_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
+        {
+          uint32_t vh[16], vl[16];
+#pragma unroll
+          for (int w = 0; w < 16; ++w) { vh[w] = pack_hi(v[2 * w], v[2 * w + 1]); vl[w] = pack_lo(v[2 * w], v[2 * w + 1], vh[w]); }
+          tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
+          tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
+          tc::tmem_st_wait();
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(vn_ready);
+        }
       }
       if (warp == 4 && lane == 0) TRACE(8, c);
       if (!tc::mbar_wait(dh_full, cp, abort_flag)) { alive = false; break; }
@@ -626,20 +644,19 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         // this thread's row d, tokens [32 half, 32 half + 32)
-#pragma unroll
-        for (int q4 = 0; q4 < 2; ++q4) {
-          uint32_t o1[16], o2[16];
-          tc::tmem_ld16(lane_addr + TM_O1 + 32 * half + 16 * q4, o1);
-          tc::tmem_ld16(lane_addr + TM_O2 + 32 * half + 16 * q4, o2);
+        {
+          uint32_t o1[32], o2[32];
+          tc::tmem_ld32(lane_addr + TM_O1 + 32 * half, o1);
+          tc::tmem_ld32(lane_addr + TM_O2 + 32 * half, o2);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * half + 16 * q4 + 4 * j4);
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * half + 4 * j4);
             const float qv[4] = {qs.x, qs.y, qs.z, qs.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j = 4 * j4 + e;
-              staging[(16 * q4 + j) * D + d] = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
+              staging[j * D + d] = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
             }
           }
         }

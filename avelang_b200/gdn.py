@@ -23,7 +23,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "read_status"]
+__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "causal_conv1d_silu", "gate_beta",
+           "read_status"]
 
 _status_words: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -247,3 +248,64 @@ def gated_rmsnorm(x, z, weight=None, eps=1e-6, *, gate_first=False, out=None):
         rc = _lib.load().ave_gdn_gated_rmsnorm(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "gated_rmsnorm")
     return out
+
+
+def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, *, out=None):
+    """Depthwise causal convolution over time followed by SiLU: ``y[t, c] = silu(bias[c] + sum_j weight[c, j] *
+    x[t - (W-1) + j, c])`` with zero history at the start of every sequence.  ``x``: bf16 ``[B, T, C]`` (channel
+    stride 1, row stride free, so a column slice of a wider projection output is accepted), ``weight``: bf16
+    ``[C, W]`` with W in 2..4, optional ``bias`` bf16 ``[C]``, optional int32 ``cu_seqlens`` (``B == 1``)."""
+    _req(x.dtype == torch.bfloat16 and x.dim() == 3 and x.is_cuda, "x must be a bf16 CUDA tensor [B, T, C]")
+    _req(x.stride(2) == 1, "x must be contiguous in its last dimension")
+    B, T, Cn = x.shape
+    _req(weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[0] == Cn and weight.device == x.device,
+         f"weight must be a bf16 tensor [{Cn}, W] on {x.device}")
+    W = weight.shape[1]
+    _req(2 <= W <= 4, f"kernel width must be 2, 3 or 4, got {W}.")
+    _req(Cn % 8 == 0, f"channels must be a multiple of 8, got {Cn}.")
+    weight = weight.contiguous()
+    if bias is not None:
+        _req(bias.dtype == torch.bfloat16 and bias.numel() == Cn and bias.device == x.device, f"bias must be bf16 [{Cn}] on {x.device}")
+        bias = bias.contiguous()
+    if out is None:
+        out = torch.empty((B, T, Cn), dtype=torch.bfloat16, device=x.device)
+    _req(out.shape == x.shape and out.dtype == torch.bfloat16 and out.device == x.device and out.stride(2) == 1,
+         f"out must be a bf16 tensor of shape {tuple(x.shape)} on {x.device}")
+    _req(out.data_ptr() != x.data_ptr(), "out must not alias x (later tokens read earlier inputs)")
+    a = _lib.ConvArgs()
+    a.struct_size = ctypes.sizeof(_lib.ConvArgs)
+    a.x, a.w, a.y = x.data_ptr(), weight.data_ptr(), out.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.B, a.T, a.C, a.width = B, T, Cn, W
+    if cu_seqlens is not None:
+        _req(B == 1 and cu_seqlens.dtype == torch.int32 and cu_seqlens.device == x.device and cu_seqlens.is_contiguous(),
+             "cu_seqlens must be a contiguous int32 tensor on the device of x, with B == 1")
+        a.cu_seqlens, a.n_seqs = cu_seqlens.data_ptr(), cu_seqlens.numel() - 1
+    a.x_stride_b, a.x_stride_t, a.y_stride_b, a.y_stride_t = x.stride(0), x.stride(1), out.stride(0), out.stride(1)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().ave_gdn_conv1d_silu(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "causal_conv1d_silu")
+    return out
+
+
+def gate_beta(a_in, b_in, A_log, dt_bias):
+    """``g = -exp(A_log) * softplus(a + dt_bias)`` and ``beta = sigmoid(b)`` in fp32.  ``a_in``, ``b_in``: bf16
+    ``[..., Hv]`` (last dimension contiguous, one common row stride); ``A_log``, ``dt_bias``: ``[Hv]``."""
+    _req(a_in.dtype == torch.bfloat16 and b_in.dtype == torch.bfloat16 and a_in.is_cuda, "a and b must be bf16 CUDA tensors")
+    _req(a_in.shape == b_in.shape and a_in.stride(-1) == 1 and b_in.stride(-1) == 1, "a and b must share a shape [..., Hv]")
+    Hv = a_in.shape[-1]
+    a2, b2 = a_in.reshape(-1, Hv) if a_in.dim() != 2 else a_in, b_in.reshape(-1, Hv) if b_in.dim() != 2 else b_in
+    _req(a2.data_ptr() == a_in.data_ptr() and b2.data_ptr() == b_in.data_ptr(), "a and b must be viewable as [rows, Hv]")
+    A_log, dt_bias = A_log.detach().float().contiguous(), dt_bias.detach().float().contiguous()
+    _req(A_log.numel() == Hv and dt_bias.numel() == Hv and A_log.device == a_in.device, f"A_log and dt_bias must have {Hv} elements")
+    g = torch.empty(a_in.shape, dtype=torch.float32, device=a_in.device)
+    beta = torch.empty_like(g)
+    s = _lib.GateArgs()
+    s.struct_size = ctypes.sizeof(_lib.GateArgs)
+    s.a, s.b, s.A_log, s.dt_bias, s.g, s.beta = (a2.data_ptr(), b2.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(),
+                                                 g.data_ptr(), beta.data_ptr())
+    s.rows, s.Hv, s.a_stride_row, s.b_stride_row = a2.shape[0], Hv, a2.stride(0), b2.stride(0)
+    with torch.cuda.device(a_in.device):
+        rc = _lib.load().ave_gdn_gate_beta(ctypes.byref(s), torch.cuda.current_stream(a_in.device).cuda_stream)
+    _lib.check(rc, "gate_beta")
+    return g, beta

@@ -200,6 +200,29 @@ def gate_beta(a, b, A_log, dt_bias, dtype=torch.float64):
     return -torch.exp(A_log) * F.softplus(a + dt_bias), torch.sigmoid(b)
 
 
+def gdn_block_ref(x, w_in, conv_w, A_log, dt_bias, norm_weight, *, Hk, Hv, dk, dv, cu_seqlens=None,
+                  round_bf16=True, dtype=torch.float64):
+    """Whole block on the CPU: in-projection [q | k | v | z | b | a] -> causal conv1d + SiLU on q/k/v -> q/k L2 norm ->
+    gate/beta -> token recurrence -> gated RMSNorm.  With ``round_bf16`` the projection and convolution outputs are
+    rounded to bf16 where the device pipeline stores them as bf16, so the comparison isolates kernel error."""
+    B, T, hidden = x.shape
+    rb = (lambda t: t.to(torch.bfloat16).to(dtype)) if round_bf16 else (lambda t: t)
+    y = rb(x.to(dtype) @ w_in.to(dtype).T)
+    nq = nk = Hk * dk
+    nv = Hv * dv
+    qkv = rb(causal_conv1d_silu(y[..., : nq + nk + nv], conv_w, cu_seqlens, dtype=dtype))
+    z = y[..., nq + nk + nv: nq + nk + 2 * nv].reshape(B, T, Hv, dv)
+    b_in = y[..., nq + nk + 2 * nv: nq + nk + 2 * nv + Hv]
+    a_in = y[..., nq + nk + 2 * nv + Hv: nq + nk + 2 * nv + 2 * Hv]
+    q = l2norm(qkv[..., :nq].reshape(B, T, Hk, dk))
+    k = l2norm(qkv[..., nq: nq + nk].reshape(B, T, Hk, dk))
+    v = qkv[..., nq + nk:].reshape(B, T, Hv, dv)
+    g, beta = gate_beta(a_in, b_in, A_log, dt_bias, dtype=dtype)
+    g, beta = g.float().to(dtype), beta.float().to(dtype)  # the device stores g and beta in fp32
+    o, _ = naive_recurrent_gated_delta_rule(q, k, v, g, beta, dk ** -0.5, None, cu_seqlens, dtype=dtype)
+    return gated_rmsnorm(o, z, norm_weight, dtype=dtype)
+
+
 def rel_l2(x: torch.Tensor, ref: torch.Tensor) -> float:
     x, ref = x.double(), ref.double()
     den = ref.norm().item()

@@ -1,0 +1,37 @@
+"""GPU test of the head-sharded GDN block (projection -> conv -> delta rule -> gated norm) against the CPU checker."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(hidden, Hk, Hv, d, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n_out = 2 * Hk * d + 2 * Hv * d + 2 * Hv
+    w_in = (0.02 * torch.randn(n_out, hidden, generator=g)).bfloat16()
+    # b/a rows drive sigmoid and softplus: give them a visible range
+    w_in[-2 * Hv:] = (0.2 * torch.randn(2 * Hv, hidden, generator=g)).bfloat16()
+    conv_w = (torch.randn(2 * Hk * d + Hv * d, 4, generator=g) / 2).bfloat16()
+    A_log = torch.rand(Hv, generator=g) * 2.77
+    dt_bias = 0.1 * torch.randn(Hv, generator=g)
+    norm_w = 1.0 + 0.1 * torch.randn(d, generator=g)
+    return w_in, conv_w, A_log, dt_bias, norm_w
+
+
+def test_block_matches_checker_and_shards_compose(built_lib, checker):
+    O, _ = checker
+    from avelang_b200.block import GdnBlockShard
+    hidden, Hk, Hv, d, B, T = 256, 2, 4, 128, 2, 200
+    w_in, conv_w, A_log, dt_bias, norm_w = _params(hidden, Hk, Hv, d)
+    x = torch.randn(B, T, hidden, generator=torch.Generator().manual_seed(1)).bfloat16()
+    full = GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d)
+    y = full.forward(x.cuda())
+    ref = O.gdn_block_ref(x, w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d)
+    # block-level tolerance: the bf16 projection and convolution outputs of the device pipeline differ from the
+    # checker's by a rounding step in a few per cent of their elements (different fp32 summation order)
+    err = O.rel_l2(y.float().cpu(), ref.bfloat16().float())
+    assert err < 5e-3, err
+    # two head shards, run one after the other on this GPU, reproduce the unsharded result
+    parts = [GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d, rank=r, world=2).forward_local(x.cuda())
+             for r in range(2)]
+    assert O.rel_l2(torch.cat(parts, 2).float().cpu(), y.float().cpu()) < 1e-6

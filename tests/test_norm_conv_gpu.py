@@ -35,3 +35,47 @@ def test_gated_rmsnorm(gdn, checker, d, gate_first):
 def test_gated_rmsnorm_empty(gdn):
     x = torch.zeros(0, 4, 128, dtype=torch.bfloat16, device="cuda")
     assert gdn.gated_rmsnorm(x, x).shape == (0, 4, 128)
+
+
+@pytest.mark.parametrize("width", [2, 3, 4])
+def test_causal_conv1d_silu(gdn, checker, width):
+    O, _ = checker
+    g = torch.Generator().manual_seed(width)
+    x = torch.randn(2, 150, 96, generator=g).bfloat16()
+    w = (torch.randn(96, width, generator=g) / 2).bfloat16()
+    bias = torch.randn(96, generator=g).bfloat16()
+    y = gdn.causal_conv1d_silu(x.cuda(), w.cuda())
+    assert O.rel_l2(y.float().cpu(), O.causal_conv1d_silu(x, w).bfloat16().float()) < 1e-3
+    yb = gdn.causal_conv1d_silu(x.cuda(), w.cuda(), bias.cuda())
+    ref = O.causal_conv1d_silu(x, w)  # bias enters before the SiLU: recompute by hand
+    xs = x.double()
+    acc = torch.zeros_like(xs)
+    for j in range(width):
+        sh = width - 1 - j
+        acc[:, sh:] += xs[:, : xs.shape[1] - sh] * w.double()[:, j]
+    acc = acc + bias.double()
+    assert O.rel_l2(yb.float().cpu(), (acc * torch.sigmoid(acc)).bfloat16().float()) < 1e-3
+    assert ref.shape == y.shape
+
+
+def test_causal_conv1d_varlen_and_column_slice(gdn, checker):
+    O, _ = checker
+    g = torch.Generator().manual_seed(0)
+    wide = torch.randn(1, 300, 160, generator=g).bfloat16()
+    w = (torch.randn(64, 4, generator=g) / 2).bfloat16()
+    cu = torch.tensor([0, 1, 3, 64, 65, 200, 300], dtype=torch.int32)
+    x = wide[:, :, 32:96]  # a column slice of a wider tensor: row stride 160
+    y = gdn.causal_conv1d_silu(x.cuda(), w.cuda(), cu_seqlens=cu.cuda())
+    assert O.rel_l2(y.float().cpu(), O.causal_conv1d_silu(x, w, cu).bfloat16().float()) < 1e-3
+
+
+def test_gate_beta(gdn, checker):
+    O, _ = checker
+    g = torch.Generator().manual_seed(0)
+    wide = (torch.randn(500, 24, generator=g) * 3).bfloat16()
+    A_log, dt_bias = torch.rand(8, generator=g) * 2.77, 0.1 * torch.randn(8, generator=g)
+    a_in, b_in = wide[:, 16:24], wide[:, 8:16]
+    gg, beta = gdn.gate_beta(a_in.cuda(), b_in.cuda(), A_log.cuda(), dt_bias.cuda())
+    g_ref, beta_ref = O.gate_beta(a_in, b_in, A_log, dt_bias)
+    assert O.rel_l2(gg.cpu(), g_ref) < 1e-5 and O.rel_l2(beta.cpu(), beta_ref) < 1e-5
+    assert (gg <= 0).all()
