@@ -83,14 +83,23 @@ struct GdnMaps {
 // K, 64..127 = Q) and the K rows alone as its N = 64 B operand: lanes 0..63 of the accumulator are K K^T, lanes
 // 64..127 are Q K^T.
 constexpr int PREP_THREADS = 256;
-constexpr int PP_KQ = 0, PP_V = 32768, PP_A = 49152, PP_SC = PP_A + C * C * 4, PP_BARS = PP_SC + 4 * C * 4;
+constexpr int U_LD = 68;                              // row stride (floats) of U^T: 16-byte rows, conflict-free float4 reads
+constexpr int U_REC_BYTES = D * U_LD * 4;             // 34816
+constexpr int PP_KQ = 0, PP_V = 32768, PP_T = 49152,  // PP_T: Tw_hi | Tw_lo | Tu_hi | Tu_lo, bf16 [64][64] K-major tiles
+              PP_A = PP_T + 4 * 8192, PP_SC = PP_A + C * C * 4, PP_BARS = PP_SC + 4 * C * 4;
 constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
+constexpr uint32_t PT_GRAM = 0, PT_W = 64, PT_U = 128;  // TMEM columns (256 allocated)
 
+// Pass 1 per (chunk, value head):
+//   tensor cores: [K; Q] K^T                                   -> A (strict lower, gated) and P (lower, gated)
+//   CUDA cores  : T = (I + A)^-1 by forward substitution (4 threads per column, rows interleaved mod 4)
+//   tensor cores: W^T = K^T (T diag(beta e^b))^T,  U^T = V^T (T diag(beta))^T   (M = 128 = d_k / d_v, N = 64 tokens)
+// W^T leaves as bf16 hi + lo [128][64] (the scan reads it as an MN-major B operand), U^T as fp32 [128][68].
 __global__ void __launch_bounds__(PREP_THREADS, 2)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][64], row i holds A[i][0..i-1]
+  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][64], row i holds A[i][0..i-1], zero elsewhere
   float* bs = reinterpret_cast<float*>(smem + PP_SC);
   float* betas = bs + C;
   float* qn = betas + C;
@@ -98,7 +107,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_BARS);
   uint64_t* tma_bar = bars;
   uint64_t* mma_bar = bars + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* mma2_bar = bars + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -111,6 +121,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   if (tid == 0) {
     tc::mbar_init(tma_bar, 1);
     tc::mbar_init(mma_bar, 1);
+    tc::mbar_init(mma2_bar, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::mbar_expect_tx(tma_bar, 32768 + 16384);
@@ -119,8 +130,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::tma_load_4d(smem + PP_KQ + 16384, &maps.k, tma_bar, 64, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 24576, &maps.q, tma_bar, 64, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_V + 8192, &maps.v, tma_bar, 64, h, cr.t0, cr.b);
   }
-  if (warp == 0) tc::tmem_alloc(tmem_slot, 64);
+  if (warp == 0) tc::tmem_alloc(tmem_slot, 256);
   if (tid < C) {
     const bool valid = tid < cr.len;
     const int64_t off = cr.b * a.g_stride_b + (int64_t)(cr.t0 + tid) * a.g_stride_t + h;
@@ -131,7 +143,16 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  if (tid == 0) { float run = 0.f; for (int i = 0; i < C; ++i) { run += bs[i]; bs[i] = run; } }
+  if (warp == 1) {  // in-chunk cumulative gate: inclusive scan of 64 values by one warp
+    float v0 = bs[lane], v1 = bs[32 + lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t0 = __shfl_up_sync(0xffffffffu, v0, o), t1 = __shfl_up_sync(0xffffffffu, v1, o);
+      if (lane >= o) { v0 += t0; v1 += t1; }
+    }
+    v1 += __shfl_sync(0xffffffffu, v0, 31);
+    bs[lane] = v0; bs[32 + lane] = v1;
+  }
 
   bool ok = tc::mbar_wait(tma_bar, 0, abort_flag);
   if (warp == 0) {
@@ -143,7 +164,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const uint64_t d = tc::smem_desc_sw128(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-        tc::mma_ss(tm, d, d, idesc, k != 0 ? 1u : 0u);
+        tc::mma_ss(tm + PT_GRAM, d, d, idesc, k != 0 ? 1u : 0u);
       }
       tc::mma_commit(mma_bar);
     }
@@ -186,15 +207,20 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     const int quarter = warp & 3, colhalf = warp >> 2;
     const int r = quarter * 32 + lane;
     uint32_t acc[32];
-    tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
+    tc::tmem_ld32(tm + PT_GRAM + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
     tc::tmem_ld_wait();
     if (r < C) {  // A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j)
       const int i = r;
       const float bi = bs[i], fi = betas[i] * kn[i];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        const int j = 32 * colhalf + jj;
-        As[i * C + j] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[jj]) : 0.f;
+      for (int j4 = 0; j4 < 8; ++j4) {
+        float av[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 32 * colhalf + 4 * j4 + e;
+          av[e] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[4 * j4 + e]) : 0.f;
+        }
+        *reinterpret_cast<float4*>(As + i * C + 32 * colhalf + 4 * j4) = make_float4(av[0], av[1], av[2], av[3]);
       }
     } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
       const int i = r - C;
@@ -217,58 +243,124 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       }
     }
   }
+  __syncthreads();
+  // T = (I + A)^-1, column col, rows 4m + part kept in x[m].  x starts at zero and T is lower triangular, so the
+  // row-i sum needs no bounds: terms with j < col or j >= i multiply zeros.
+  {
+    const int col = tid >> 2, part = tid & 3;
+    const int first_row = (col & ~7);  // rows above the warp's first column are identically zero
+    float x[16];
+#pragma unroll
+    for (int m = 0; m < 16; ++m) x[m] = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; ++i) {
+      if (i >= first_row) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < (i + 3) / 4; ++m) {
+          const float av = As[i * C + 4 * m + part];
+          if (m & 1) s1 = fmaf(av, x[m], s1); else s0 = fmaf(av, x[m], s0);
+        }
+        float tot = s0 + s1;
+        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        const float ti = ((i == col) ? 1.f : 0.f) - tot;
+        if (part == (i & 3)) x[i >> 2] = ti;
+      }
+    }
+    // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j = col], 128-byte swizzle
+    const float fu = betas[col], fw = fu * __expf(bs[col]) * kn[col];
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      const int i = 4 * m + part;
+      const uint32_t off = (uint32_t)(i * 128 + ((((col >> 3) ^ (i & 7))) << 4) + (col & 7) * 2);
+      __nv_bfloat16 hi, lo;
+      split_bf16(x[m] * fw, hi, lo);
+      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + off) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 8192 + off) = lo;
+      split_bf16(x[m] * fu, hi, lo);
+      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 16384 + off) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 24576 + off) = lo;
+    }
+  }
+  tc::fence_proxy_async_smem();
+  __syncthreads();
+  if (warp == 0) {
+    const bool leader = tc::elect_one();
+    if (ok && leader) {
+      constexpr uint32_t idesc = tc::idesc_f16(128, 64, 1, 1, true, false);  // A MN-major (token rows), B K-major
+      const uint32_t kbase = tc::smem_u32(smem + PP_KQ), vbase = tc::smem_u32(smem + PP_V), tbase = tc::smem_u32(smem + PP_T);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // K halves sit 16384 bytes apart (Q halves are interleaved), V halves 8192 bytes apart
+          tc::mma_ss(tm + PT_W, tc::smem_desc_sw128(kbase + k * 2048, 16384, 1024), tc::smem_desc_sw128(tbase + t * 8192 + k * 32, 16, 1024),
+                     idesc, (t | k) != 0 ? 1u : 0u);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          tc::mma_ss(tm + PT_U, tc::smem_desc_sw128(vbase + k * 2048, 8192, 1024),
+                     tc::smem_desc_sw128(tbase + 16384 + t * 8192 + k * 32, 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
+        }
+      }
+      tc::mma_commit(mma2_bar);
+    }
+    __syncwarp();
+  }
+  ok = ok && tc::mbar_wait(mma2_bar, 0, abort_flag);
+  tc::tc_fence_after_sync();
+  {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // d_k index (warps 0..3) or d_v index (warps 4..7)
+    const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
+    if (warp < 4) {
+      uint4* wh = reinterpret_cast<uint4*>(out.w_hi + rec * (C * D) + r * C);
+      uint4* wl = reinterpret_cast<uint4*>(out.w_lo + rec * (C * D) + r * C);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t acc[32];
+        tc::tmem_ld32(lane_addr + PT_W + 32 * half, acc);
+        tc::tmem_ld_wait();
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int w = 0; w < 16; ++w) {
+          const float v0 = __uint_as_float(acc[2 * w]), v1 = __uint_as_float(acc[2 * w + 1]);
+          hi[w] = pack_bf16x2(v0, v1);
+          lo[w] = pack_bf16x2(v0 - __uint_as_float(hi[w] << 16), v1 - __uint_as_float(hi[w] & 0xffff0000u));
+        }
+        if (ok) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            wh[4 * half + v4] = make_uint4(hi[4 * v4], hi[4 * v4 + 1], hi[4 * v4 + 2], hi[4 * v4 + 3]);
+            wl[4 * half + v4] = make_uint4(lo[4 * v4], lo[4 * v4 + 1], lo[4 * v4 + 2], lo[4 * v4 + 3]);
+          }
+        }
+      }
+    } else {
+      uint4* up = reinterpret_cast<uint4*>(out.u + rec * (D * U_LD) + r * U_LD);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t acc[32];
+        tc::tmem_ld32(lane_addr + PT_U + 32 * half, acc);
+        tc::tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+          for (int v4 = 0; v4 < 8; ++v4) up[8 * half + v4] = make_uint4(acc[4 * v4], acc[4 * v4 + 1], acc[4 * v4 + 2], acc[4 * v4 + 3]);
+        }
+      }
+    }
+  }
   tc::tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tm, 64);
+    tc::tmem_dealloc(tm, 256);
   }
-  if (!ok) {
-    if (tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
-    return;
-  }
-  // forward substitution, one column of [W | U] per thread
-  {
-    const int col = tid;
-    const bool is_w = col < D;
-    const int cc = col & (D - 1);
-    // element (i, cc) of the swizzled K tile / of the plain V tile
-    const uint8_t* kcol = smem + PP_KQ + (cc >> 6) * 16384 + (cc & 7) * 2;
-    const int kchunk = (cc & 63) >> 3;
-    const __nv_bfloat16* vcol = reinterpret_cast<const __nv_bfloat16*>(smem + PP_V) + cc;
-    float x[C];
-#pragma unroll
-    for (int i = 0; i < C; ++i) {
-      float rhs;
-      if (is_w) {
-        const float kv = bf2f(*reinterpret_cast<const __nv_bfloat16*>(kcol + i * 128 + ((kchunk ^ (i & 7)) << 4)));
-        rhs = betas[i] * __expf(bs[i]) * kn[i] * kv;
-      } else {
-        rhs = betas[i] * bf2f(vcol[i * D]);
-      }
-      // A[i][j] is zero for j >= i, so whole float4 groups can be consumed; two accumulators shorten the chain
-      float r2 = 0.f;
-#pragma unroll
-      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-        const float4 av = *reinterpret_cast<const float4*>(As + i * C + 4 * j4);
-        rhs = fmaf(-av.x, x[4 * j4], rhs);
-        if (4 * j4 + 1 < i) r2 = fmaf(-av.y, x[4 * j4 + 1], r2);
-        if (4 * j4 + 2 < i) rhs = fmaf(-av.z, x[4 * j4 + 2], rhs);
-        if (4 * j4 + 3 < i) r2 = fmaf(-av.w, x[4 * j4 + 3], r2);
-      }
-      x[i] = rhs + r2;
-    }
-    if (is_w) {
-      __nv_bfloat16* wh = out.w_hi + rec * (C * D) + col;
-      __nv_bfloat16* wl = out.w_lo + rec * (C * D) + col;
-#pragma unroll
-      for (int i = 0; i < C; ++i) { __nv_bfloat16 hi, lo; split_bf16(x[i], hi, lo); wh[i * D] = hi; wl[i * D] = lo; }
-    } else {
-      float* u = out.u + rec * (C * D) + cc;
-#pragma unroll
-      for (int i = 0; i < C; ++i) u[i * D] = x[i];
-    }
-  }
+  if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
@@ -288,7 +380,7 @@ constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
 constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
 constexpr int OFF_SCAL = 2 * STAGE;                  // 2 x [qs | ks | decay]
 constexpr int OFF_U = OFF_SCAL + 2 * SCAL_BYTES;     // fp32 [64][128], single buffer
-constexpr int U_BYTES = C * D * 4;
+constexpr int U_BYTES = U_REC_BYTES;
 constexpr int OFF_STAGING = OFF_U + U_BYTES;         // fp32 [32][128]: half a chunk of output rows
 constexpr int OFF_BARS = OFF_STAGING + 32 * D * 4;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
@@ -418,10 +510,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         const int row = (int)(rec * C);
         const int tok = sp.t0 + c * C;
         tc::mbar_expect_tx(&full[s], STAGE_TX);
-        tc::tma_load_2d(st + ST_WHI, &maps.w_hi, &full[s], 0, row);
-        tc::tma_load_2d(st + ST_WHI + 8192, &maps.w_hi, &full[s], 64, row);
-        tc::tma_load_2d(st + ST_WLO, &maps.w_lo, &full[s], 0, row);
-        tc::tma_load_2d(st + ST_WLO + 8192, &maps.w_lo, &full[s], 64, row);
+        tc::tma_load_2d(st + ST_WHI, &maps.w_hi, &full[s], 0, 2 * row);  // W^T tile: 128 d_k rows of 64 tokens
+        tc::tma_load_2d(st + ST_WLO, &maps.w_lo, &full[s], 0, 2 * row);
         tc::tma_load_4d(st + ST_Q, &maps.q, &full[s], 0, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_Q + 8192, &maps.q, &full[s], 64, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_K, &maps.k, &full[s], 0, hk, tok, sp.b);
@@ -432,13 +522,13 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         // U of chunk c replaces U of chunk c-1 once the chain epilogue has consumed it
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
         tc::mbar_expect_tx(u_full, U_BYTES);
-        tc::bulk_load(smem + OFF_U, u_ws + rec * (C * D), U_BYTES, u_full);
+        tc::bulk_load(smem + OFF_U, u_ws + rec * (D * U_LD), U_BYTES, u_full);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (whole warp runs the loop,
     // one elected lane issues)
-    constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, false, true, false);   // negated A
+    constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, true, true, false);    // negated A, B = W^T read MN-major
     constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
     constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
     for (int c = 0; c < n_chunks; ++c) {
@@ -451,10 +541,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       TRACE(1, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
-        // Vn^T accumulator = -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); a K-major tile is two 64-wide halves 8 KB apart
-        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 32, 8192 - 128, 16, id_vn, 8, false);
-        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 32, 8192 - 128, 16, id_vn, 8, true);
-        issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 32, 8192 - 128, 16, id_vn, 8, true);
+        // Vn^T accumulator = -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); W^T is one [128 d_k][64 token] tile, 16 d_k rows per step
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 2048, 0, 16, id_vn, 8, false);
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 2048, 0, 16, id_vn, 8, true);
+        issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
         tc::mma_commit(vn_full);
       }
       __syncwarp();
@@ -545,7 +635,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tmem_ld32(lane_addr + TM_VN + 32 * grp, acc);
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = u_s[(32 * grp + j) * D + d];
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 uq = *reinterpret_cast<const float4*>(u_s + d * U_LD + 32 * grp + 4 * j4);
+          v[4 * j4] = uq.x; v[4 * j4 + 1] = uq.y; v[4 * j4 + 2] = uq.z; v[4 * j4 + 3] = uq.w;
+        }
         tc::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(acc[j]);
@@ -741,7 +834,7 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   L.w_lo = off; off = up(off + recs * REC_W);
   L.p_hi = off; off = up(off + recs * REC_P);
   L.p_lo = off; off = up(off + recs * REC_P);
-  L.u = off; off = up(off + recs * (size_t)(C * D * 4));
+  L.u = off; off = up(off + recs * (size_t)U_REC_BYTES);
   L.scal = off; off = up(off + recs * (size_t)(SCAL_FLOATS * 4));
   L.total = off;
   return L;
@@ -773,11 +866,11 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
   GdnMaps maps;
   const uint64_t rows = (uint64_t)L.chunks * a.Hv * C;
   {
-    const uint64_t dw[2] = {D, rows}, sw[2] = {2, D * 2}, dp[2] = {C, rows}, spp[2] = {2, C * 2};
-    const uint32_t box[2] = {64, 64};
+    const uint64_t dw[2] = {C, 2 * rows}, sw[2] = {2, C * 2}, dp[2] = {C, rows}, spp[2] = {2, C * 2};
+    const uint32_t box[2] = {64, 64}, boxw[2] = {64, 128};
     int rc;
-    if ((rc = make_tmap(&maps.w_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_hi, 2, dw, sw, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    if ((rc = make_tmap(&maps.w_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_lo, 2, dw, sw, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&maps.w_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_hi, 2, dw, sw, boxw, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&maps.w_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_lo, 2, dw, sw, boxw, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.p_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.p_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     const uint32_t box4[4] = {64, 1, 64, 1};
@@ -786,10 +879,10 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
     const uint64_t sk[4] = {2, (uint64_t)a.k_stride_h * 2, (uint64_t)a.k_stride_t * 2, (uint64_t)(a.B > 1 ? a.k_stride_b : a.k_stride_t * a.T) * 2};
     if ((rc = make_tmap(&maps.q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.q), 4, dq, sq, box4, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.k), 4, dq, sk, box4, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    const uint32_t boxv[4] = {D, 1, 64, 1};
+    const uint32_t boxv[4] = {64, 1, 64, 1};
     const uint64_t dv4[4] = {D, (uint64_t)a.Hv, (uint64_t)a.T, (uint64_t)a.B};
     const uint64_t sv[4] = {2, (uint64_t)a.v_stride_h * 2, (uint64_t)a.v_stride_t * 2, (uint64_t)(a.B > 1 ? a.v_stride_b : a.v_stride_t * a.T) * 2};
-    if ((rc = make_tmap(&maps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.v), 4, dv4, sv, boxv, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if ((rc = make_tmap(&maps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.v), 4, dv4, sv, boxv, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
 
   if (a.cu_seqlens != nullptr) chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start);
