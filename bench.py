@@ -249,6 +249,25 @@ def workload_config(n):
             "l2": "256 MiB flush write before every timed step; inputs 272 MB > 126 MB L2"}
 
 
+def profile_case(name: str):
+    """Small fixed cases for profiler captures (a few launches, a few hundred MB on the device at most)."""
+    from avelang_b200 import gdn, synth
+    torch.cuda.set_device(0)
+    if name == "decode":
+        inp = synth.config2().to("cuda")
+        for _ in range(3):
+            gdn.fused_recurrent_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, initial_state=inp.state_pool,
+                                                 state_indices=inp.state_indices)
+    elif name == "prefill2048":
+        inp = synth.config1(T=2048).to("cuda")
+        for _ in range(2):
+            gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, output_final_state=True, z=inp.z)
+    else:
+        raise SystemExit(f"unknown profile case {name!r}")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "done": True}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -257,7 +276,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048"],
+                    help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
+    if args.profile_case:
+        return profile_case(args.profile_case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
