@@ -207,11 +207,16 @@ def bench_decode(steps=1000, warmup=20):
     return us, state_bytes, state_bytes + other
 
 
-def cpu_baseline(sample_tokens=T_PREFILL, reps=3):
-    """The C restatement of the token recurrence (fp32, OpenMP over sequence x head) on the host cores."""
+def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0):
+    """The C restatement of the token recurrence (fp32, OpenMP over sequence x head) on the host cores; repeated
+    until about `budget_s` seconds of CPU work have been timed (or `reps` runs)."""
     from avelang_b200 import synth
     from oracle import c_oracle
     inp = synth.config1(T=sample_tokens)
+    t = time.perf_counter()
+    c_oracle.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, precision="f32")  # untimed warm-up
+    if reps is None:
+        reps = max(3, min(100, int(budget_s / max(time.perf_counter() - t, 1e-3))))
     times = []
     for _ in range(reps):
         t = time.perf_counter()
@@ -227,10 +232,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    for _ in range(min(args.warmup, 1)):
-        cpu_baseline(reps=1)
     t = time.perf_counter()
-    base = cpu_baseline(reps=max(1, min(args.steps, 5)))
+    base = cpu_baseline(reps=max(3, args.steps))
     wall = time.perf_counter() - t
     line = {"impl": "reference", "metric": "gdn_prefill_tokens_per_s", "value": base["value"], "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -247,6 +250,73 @@ def workload_config(n):
                         "chunk 64, bf16 q/k/v/z, fp32 g/beta, fused gated RMSNorm, fp32 final state",
             "global_batch": n, "seq_len": T_PREFILL, "parallelism": f"sequence-sharded x{n}, no collective",
             "l2": "256 MiB flush write before every timed step; inputs 272 MB > 126 MB L2"}
+
+
+def bench_varlen(args, rank, world):
+    """Packed varlen prefill (64 sequences, log-uniform lengths in [128, 16384], 262144 tokens, nonzero initial
+    states, final states returned), value heads sharded Hv/G per rank, no collective: strong scaling."""
+    from avelang_b200 import gdn, synth
+    from avelang_b200.block import HeadShard
+    inp = synth.config3()
+    sh = HeadShard(rank, world, HK, HV)
+    ks, vs = slice(sh.key_heads.start, sh.key_heads.stop), slice(sh.value_heads.start, sh.value_heads.stop)
+    q, k, v = inp.q[:, :, ks].contiguous().cuda(), inp.k[:, :, ks].contiguous().cuda(), inp.v[:, :, vs].contiguous().cuda()
+    g, beta = inp.g[:, :, vs].contiguous().cuda(), inp.beta[:, :, vs].contiguous().cuda()
+    s0, cu = inp.initial_state[:, vs].contiguous().cuda(), inp.cu_seqlens.cuda()
+    out = torch.empty_like(v)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    step = lambda: gdn.chunk_gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=True, cu_seqlens=cu, out=out)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
+    ms = total_ms / args.steps
+    chunks = sum((n + 63) // 64 for n in inp.extras["lengths"])
+    flops = chunks * HV * FLOP_PER_CHUNK_HEAD
+    peaks = measured_peaks()
+    tokens = int(inp.cu_seqlens[-1])
+    achieved = flops / (ms * 1e-3) / 1e12
+    return {"metric": "gdn_varlen_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 in / fp32 state and accumulate", "data": "synthetic",
+            "config": {"workload": f"varlen packed prefill, 64 seqs, {tokens} tokens, {chunks} chunks, Hk=16, Hv=32, d=128, "
+                                   "initial and final states", "parallelism": f"value heads sharded x{world}, no collective",
+                       "l2": "256 MiB flush write before every timed step"},
+            "gpu_launches": 3 * args.steps, "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"] * world, "unit": "TFLOP/s",
+                         "frac": achieved / (peaks["bf16_tflops"] * world), "traffic": None,
+                         "peak_source": peaks["source"] + " (burst) x n_gpus"}}
+
+
+def bench_block(args, rank, world):
+    """Full GDN block, B=4, T=32768, hidden 2048: in-projection, conv1d+SiLU, L2 norm, gate/beta, chunked delta rule,
+    gated RMSNorm on this rank's heads, then the NCCL all-gather of head outputs: strong scaling."""
+    from avelang_b200.block import GdnBlockShard
+    B, T, hidden = 4, 32768, 2048
+    gen = torch.Generator().manual_seed(0)
+    n_out = 2 * HK * D + 2 * HV * D + 2 * HV
+    w_in = (0.02 * torch.randn(n_out, hidden, generator=gen)).bfloat16()
+    conv_w = (torch.randn(2 * HK * D + HV * D, 4, generator=gen) / 2).bfloat16()
+    A_log = torch.rand(HV, generator=gen) * 2.7726
+    dt_bias = 0.1 * torch.randn(HV, generator=gen)
+    x = torch.randn(B, T, hidden, generator=gen).bfloat16().cuda()
+    blk = GdnBlockShard(w_in, conv_w, A_log, dt_bias, torch.ones(D), Hk=HK, Hv=HV, dk=D, dv=D, rank=rank, world=world)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    step = lambda: blk.forward(x)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
+    ms = total_ms / args.steps
+    flops = 2 * B * T * hidden * n_out + (B * T // 64) * HV * FLOP_PER_CHUNK_HEAD
+    peaks = measured_peaks()
+    achieved = flops / (ms * 1e-3) / 1e12
+    return {"metric": "gdn_block_tokens_per_s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "GDN block B=4 T=32768 hidden 2048: in-proj, conv1d k=4 + SiLU, L2 norm, gate/beta, "
+                                   "chunked delta rule, gated RMSNorm, head all-gather",
+                       "parallelism": f"heads sharded x{world}, one NCCL all-gather", "l2": "256 MiB flush write before every timed step"},
+            "gpu_launches": 6 * args.steps, "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] * world, "unit": "TFLOP/s",
+                         "frac": achieved / (peaks["bf16_tflops_sustained"] * world), "traffic": None,
+                         "peak_source": peaks["source"] + " (sustained) x n_gpus"}}
 
 
 def profile_case(name: str):
@@ -276,6 +346,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block"],
+                    help="prefill (default, the headline line), varlen (head-sharded packed prefill) or block")
     ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048"],
                     help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
@@ -290,6 +362,13 @@ def main():
     _lib.load()  # fail loudly when the CUDA library is missing
     rank, world, local = dist_setup(args.gpus)
     peaks = measured_peaks()
+    if args.workload != "prefill":
+        line = (bench_varlen if args.workload == "varlen" else bench_block)(args, rank, world)
+        if rank == 0:
+            print(json.dumps(line))
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
 
     ms, clocks, e2e_ms, h2d, d2h = bench_prefill(args, rank, world)
     tokens = T_PREFILL * world
@@ -301,7 +380,7 @@ def main():
             "config": workload_config(world),
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": 3 * args.steps, "clocks": clocks}
+            "gpu_launches": 2 * args.steps, "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                         "frac": achieved / peaks["bf16_tflops"], "traffic": None,
