@@ -280,7 +280,7 @@ def bench_varlen(args, rank, world):
             "config": {"workload": f"varlen packed prefill, 64 seqs, {tokens} tokens, {chunks} chunks, Hk=16, Hv=32, d=128, "
                                    "initial and final states", "parallelism": f"value heads sharded x{world}, no collective",
                        "l2": "256 MiB flush write before every timed step"},
-            "gpu_launches": 3 * args.steps, "clocks": clocks,
+            "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"] * world, "unit": "TFLOP/s",
                          "frac": achieved / (peaks["bf16_tflops"] * world), "traffic": None,
                          "peak_source": peaks["source"] + " (burst) x n_gpus"}}
@@ -313,7 +313,7 @@ def bench_block(args, rank, world):
             "config": {"workload": "GDN block B=4 T=32768 hidden 2048: in-proj, conv1d k=4 + SiLU, L2 norm, gate/beta, "
                                    "chunked delta rule, gated RMSNorm, head all-gather",
                        "parallelism": f"heads sharded x{world}, one NCCL all-gather", "l2": "256 MiB flush write before every timed step"},
-            "gpu_launches": 6 * args.steps, "clocks": clocks,
+            "gpu_launches": 6 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] * world, "unit": "TFLOP/s",
                          "frac": achieved / (peaks["bf16_tflops_sustained"] * world), "traffic": None,
                          "peak_source": peaks["source"] + " (sustained) x n_gpus"}}
