@@ -14,6 +14,7 @@ P, U32, I32, I64, U64, F32 = (ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int32, 
 OK, INVALID_ARGUMENT, UNSUPPORTED, MISALIGNED, CUDA_ERROR, WORKSPACE_TOO_SMALL = range(6)
 DEV_BAD_SLOT, DEV_BAD_SEQLEN, DEV_WAIT_EXPIRED = 1, 2, 4
 FLAG_QK_L2NORM, FLAG_GATE_FIRST = 1, 2
+NOALLOC_SCRATCH_BYTES = 64 << 20
 
 
 class GdnArgs(ctypes.Structure):
@@ -54,6 +55,7 @@ class GateArgs(ctypes.Structure):
 SYMBOLS = {
     "ave_gdn_chunk_prefill": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_prefill_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(GdnArgs)]),
+    "ave_gdn_chunk_prefill_noalloc": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_decode_step": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_gated_rmsnorm": (ctypes.c_int, [ctypes.POINTER(NormArgs), P]),
     "ave_gemm_bf16_nt": (ctypes.c_int, [ctypes.POINTER(GemmArgs), P]),

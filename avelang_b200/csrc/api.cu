@@ -47,6 +47,9 @@ static int validate_gdn(const AveGdnArgs* a, bool prefill) {
   if ((reinterpret_cast<uintptr_t>(a->g) & 3u) || (reinterpret_cast<uintptr_t>(a->beta) & 3u)) return AVE_GDN_MISALIGNED;
   return AVE_GDN_OK;
 }
+
+// Argument checks of the prefill entry points, for translation units that define further prefill variants.
+int validate_prefill_args(const AveGdnArgs* a) { return validate_gdn(a, true); }
 }  // namespace ave
 
 using namespace ave;

@@ -903,3 +903,40 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace ave
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// Some callers may not allocate device memory at all: code that runs between a framework's memory-pool snapshot
+// and its release (serving runtimes that hand every byte of HBM to a paged state/KV pool at start-up and forbid
+// later driver allocations), plug-in callbacks that only receive pre-registered buffers, and latency-critical
+// paths where an allocator call is not allowed.  For them the prefill scratch lives in this fixed array, which
+// every GPU that loads the library carries until the process exits.
+namespace ave {
+int validate_prefill_args(const AveGdnArgs* a);
+constexpr size_t kStaticScratchBytes = AVE_GDN_NOALLOC_SCRATCH_BYTES;  // 64 MiB: about 790 chunk-heads of d = 128
+}
+static __device__ __align__(256) unsigned char g_static_prefill_scratch[ave::kStaticScratchBytes];
+
+// The array's name is only a host-side handle; the device address is looked up once per device (with that device
+// current) and cached.  That first call on a device should be made outside any stream capture.
+extern "C" int ave_gdn_chunk_prefill_noalloc(const AveGdnArgs* args, void* stream) {
+  using namespace ave;
+  const int rc = validate_prefill_args(args);
+  if (rc != AVE_GDN_OK) return rc;
+  if ((int64_t)args->B * args->T == 0 || args->n_seqs == 0) return AVE_GDN_OK;
+  if (args->dk != 128 || args->dv != 128) return AVE_GDN_UNSUPPORTED;
+  if (prefill_tc_workspace_bytes(*args) > kStaticScratchBytes) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  AVE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return AVE_GDN_UNSUPPORTED;
+  if (scratch_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    AVE_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_prefill_scratch));
+    scratch_of_device[dev] = p;
+  }
+  AveGdnArgs local = *args;
+  local.workspace = scratch_of_device[dev];
+  local.workspace_bytes = kStaticScratchBytes;
+  // every scratch record a launch reads is written earlier in the same launch sequence, so nothing needs clearing
+  return launch_prefill_tc(local, reinterpret_cast<cudaStream_t>(stream));
+}

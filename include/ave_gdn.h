@@ -94,6 +94,18 @@ typedef struct AveGdnArgs {
 int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream);
 size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args);
 
+/* Same computation as ave_gdn_chunk_prefill for callers that may not allocate device memory (a serving runtime
+ * that has handed all of HBM to its paged pools, a plug-in callback limited to pre-registered buffers, a path where
+ * allocator calls are forbidden): `workspace` / `workspace_bytes` are ignored and the scratch is a fixed 64 MiB
+ * array inside the library (AVE_GDN_NOALLOC_SCRATCH_BYTES), held by every GPU that loads the library until the
+ * process exits.  Requests needing more scratch than that, i.e. more than about 790 (chunk, value head) pairs, return
+ * AVE_GDN_WORKSPACE_TOO_SMALL; only dk = dv = 128 is served.  Calls no cudaMalloc/cudaFree or other allocating routine.
+ * The first call on a device looks up the array's device address and should be made outside stream capture.  All
+ * calls share the one array: calls that overlap on the GPU (different streams) race; nothing needs clearing between
+ * calls.  This entry point has no counterpart in the reference. */
+#define AVE_GDN_NOALLOC_SCRATCH_BYTES ((size_t)64 << 20)
+int ave_gdn_chunk_prefill_noalloc(const AveGdnArgs* args, void* stream);
+
 /* Token-by-token recurrence with the state tile held on chip; T == 1 with state_indices is the
  * continuous-batching decode step (state streamed once in, once out, updated in place). */
 int ave_gdn_decode_step(const AveGdnArgs* args, void* stream);
