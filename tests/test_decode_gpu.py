@@ -57,9 +57,10 @@ def test_decode_chain_of_steps_matches_recurrence(gdn, checker):
     o_ref, s_ref = C.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, inp.initial_state)
     check_o(O, torch.cat(outs, 1), o_ref)
     check_s(O, pool[idx.long()], s_ref)
-    # the multi-token form of the same kernel gives the same bits as the chained steps
+    # the multi-token form (state kept in registers across tokens) agrees with the chained single-token steps
     o2, s2 = gdn.fused_recurrent_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, initial_state=g.initial_state)
-    assert torch.equal(o2, torch.cat(outs, 1)) and torch.equal(s2, pool[idx.long()])
+    assert O.rel_l2(o2.float().cpu(), torch.cat(outs, 1).float().cpu()) < 1e-3
+    assert O.rel_l2(s2.cpu(), pool[idx.long()].cpu()) < 1e-5
 
 
 def test_decode_varlen_l2norm_and_fused_norm(gdn, checker):
