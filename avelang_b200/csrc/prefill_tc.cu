@@ -366,11 +366,11 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 // ------------------------------------------------------------------------------------------------ pass 2
 constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA issuer; warpgroups 1,2: chain epilogue (two
                                     // column groups); warpgroup 3: output.  Launch allocation is 128 registers per thread,
-                                    // redistributed below as 56 / 160 / 160 / 136 (sum 512).
+                                    // redistributed below as 72 / 176 / 176 / 88 (sum 512).
 #ifndef AVE_REGS_CTRL
-#define AVE_REGS_CTRL 56
-#define AVE_REGS_CHAIN 160
-#define AVE_REGS_OUT 136
+#define AVE_REGS_CTRL 72
+#define AVE_REGS_CHAIN 176
+#define AVE_REGS_OUT 88
 #endif
 constexpr int REGS_CTRL = AVE_REGS_CTRL, REGS_CHAIN = AVE_REGS_CHAIN, REGS_OUT = AVE_REGS_OUT;
 static_assert(REGS_CTRL + 2 * REGS_CHAIN + REGS_OUT <= 4 * 128, "register redistribution exceeds the launch allocation");
@@ -381,8 +381,7 @@ constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
 constexpr int OFF_SCAL = 2 * STAGE;                  // 2 x [qs | ks | decay]
 constexpr int OFF_U = OFF_SCAL + 2 * SCAL_BYTES;     // fp32 [64][128], single buffer
 constexpr int U_BYTES = U_REC_BYTES;
-constexpr int OFF_STAGING = OFF_U + U_BYTES;         // fp32 [32][128]: half a chunk of output rows
-constexpr int OFF_BARS = OFF_STAGING + 32 * D * 4;
+constexpr int OFF_BARS = OFF_U + U_BYTES;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
 // TMEM columns
 constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO = 160, TM_VDHI = 192, TM_VDLO = 224,
@@ -425,11 +424,10 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
-                     const float* __restrict__ u_ws, const float* __restrict__ scal_ws) {
+                     const float* __restrict__ u_ws, const float* __restrict__ scal_ws, float* __restrict__ o_f32) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const float* u_s = reinterpret_cast<const float*>(smem + OFF_U);
-  float* staging = reinterpret_cast<float*>(smem + OFF_STAGING);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
   uint64_t* full = bars;          // [2] stage landed
   uint64_t* empty = bars + 2;     // [2] stage consumed
@@ -442,7 +440,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   uint64_t* u_full = bars + 10;
   uint64_t* u_empty = bars + 11;
   uint64_t* chain_bar = bars + 12;
-  uint64_t* out_bar = bars + 13;
   uint64_t* vd_ready = bars + 14; // Vd hi+lo written to TMEM (the state update needs nothing else)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -473,8 +470,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   }
   __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (int64_t)h * a.o_stride_h;
   if (slot < 0) {
-    for (int e = threadIdx.x; e < sp.len * D; e += SCAN_THREADS)
-      og[(int64_t)(sp.t0 + e / D) * a.o_stride_t + e % D] = __float2bfloat16(0.f);
+    for (int e = threadIdx.x; e < sp.len * D; e += SCAN_THREADS) {
+      const int64_t tok = sp.t0 + e / D;
+      if (o_f32 != nullptr) o_f32[(((int64_t)sp.b * a.T + tok) * a.Hv + h) * D + e % D] = 0.f;
+      else og[tok * a.o_stride_t + e % D] = __float2bfloat16(0.f);
+    }
     return;
   }
   const int n_chunks = (sp.len + C - 1) / C;
@@ -486,7 +486,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
     tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
     tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 8);
-    tc::mbar_init(chain_bar, 8); tc::mbar_init(out_bar, 4); tc::mbar_init(vd_ready, 8);
+    tc::mbar_init(chain_bar, 8); tc::mbar_init(vd_ready, 8);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -699,110 +699,49 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
   } else {
     tc::reg_set<REGS_OUT, 128>();
-    // ------------------------------------------------------------------ output warps: o = scale (qs_i O1 + O2), gated norm, store
-    const int ow = warp - 12;           // 0..3
+    // ------------------------------------------------------------------ output warps: o = scale (qs_i O1 + O2), straight
+    // from registers: thread = d_v row, one store per token (a warp covers 32 adjacent features of one token).  When a
+    // gated norm follows, the un-normalised output is kept in fp32 scratch for the norm kernel; otherwise it is the result.
     const int quarter = warp & 3;
     const int d = quarter * 32 + lane;
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
-    const __nv_bfloat16* zg = a.z ? reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (int64_t)h * a.z_stride_h + 4 * lane
-                                  : nullptr;
-    const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
-    float nw[4] = {1.f, 1.f, 1.f, 1.f};
-    if (a.norm_weight != nullptr) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) nw[e] = a.norm_weight[4 * lane + e];
-    }
-    uint32_t sync_phase = 0;
+    float* of = o_f32 ? o_f32 + ((int64_t)sp.b * a.T * a.Hv + h) * D + d : nullptr;
     bool alive = true;
     for (int c = 0; c < n_chunks && alive; ++c) {
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + s * SCAL_BYTES);
       const int len = min(C, sp.len - c * C);
-      // gate rows of this warp's output tokens (8 per half chunk), issued before the accumulators are complete
-      uint2 zraw[2][8];
-      if (zg != nullptr) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half)
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const int i = 32 * half + ow * 8 + r;
-            zraw[half][r] = (i < len) ? *reinterpret_cast<const uint2*>(zg + (int64_t)(sp.t0 + c * C + i) * a.z_stride_t) : make_uint2(0u, 0u);
-          }
-      }
+      const int64_t tok0 = sp.t0 + c * C;
       if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
       if (!tc::mbar_wait(o_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 12 && lane == 0) TRACE(11, c);
       tc::tc_fence_after_sync();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        // this thread's row d, tokens [32 half, 32 half + 32)
-        {
-          uint32_t o1[32], o2[32];
-          tc::tmem_ld32(lane_addr + TM_O1 + 32 * half, o1);
-          tc::tmem_ld32(lane_addr + TM_O2 + 32 * half, o2);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * half + 4 * j4);
-            const float qv[4] = {qs.x, qs.y, qs.z, qs.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 4 * j4 + e;
-              staging[j * D + d] = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
-            }
-          }
-        }
-        if (half == 1) {  // both accumulators fully drained
+      for (int part = 0; part < 2; ++part) {
+        uint32_t o1[32], o2[32];
+        tc::tmem_ld32(lane_addr + TM_O1 + 32 * part, o1);
+        tc::tmem_ld32(lane_addr + TM_O2 + 32 * part, o2);
+        tc::tmem_ld_wait();
+        if (part == 1) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
           tc::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
         }
-        if (half == 0 && warp == 12 && lane == 0) TRACE(13, c);
-        if (!group_sync(out_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
-        if (half == 0 && warp == 12 && lane == 0) TRACE(14, c);
-        {
-          float o4[8][4], gz[8][4], ss[8];
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const float4 ov = *reinterpret_cast<const float4*>(staging + (ow * 8 + r) * D + 4 * lane);
-            o4[r][0] = ov.x; o4[r][1] = ov.y; o4[r][2] = ov.z; o4[r][3] = ov.w;
-            if (zg != nullptr) {
-              float zz[4];
-              unpack_bf16x4(zraw[half][r], zz);
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * part + 4 * j4);
+          const float qv[4] = {qs.x, qs.y, qs.z, qs.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e) gz[r][e] = silu(zz[e]);
-              if (gate_first) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { o4[r][e] *= gz[r][e]; gz[r][e] = 1.0f; }
-              }
-              ss[r] = o4[r][0] * o4[r][0] + o4[r][1] * o4[r][1] + o4[r][2] * o4[r][2] + o4[r][3] * o4[r][3];
+          for (int e = 0; e < 4; ++e) {
+            const int j = 4 * j4 + e, i = 32 * part + j;
+            const float ov = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
+            if (i < len) {
+              if (of != nullptr) of[(tok0 + i) * ((int64_t)a.Hv * D)] = ov;
+              else og[(tok0 + i) * a.o_stride_t + d] = __float2bfloat16(ov);
             }
-          }
-          if (zg != nullptr) {
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-              for (int r = 0; r < 8; ++r) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], off);
-            }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              const float rinv = rsqrtf(ss[r] * (1.0f / D) + a.norm_eps);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) o4[r][e] = o4[r][e] * rinv * nw[e] * gz[r][e];
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const int i = 32 * half + ow * 8 + r;
-            if (i < len)
-              *reinterpret_cast<uint2*>(og + (int64_t)(sp.t0 + c * C + i) * a.o_stride_t + 4 * lane) =
-                  make_uint2(pack_bf16x2(o4[r][0], o4[r][1]), pack_bf16x2(o4[r][2], o4[r][3]));
           }
         }
-        if (half == 0 && warp == 12 && lane == 0) TRACE(15, c);
-        // staging may be overwritten by the next half
-        if (!group_sync(out_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
       }
       if (lane == 0) tc::mbar_arrive(&empty[s]);
       if (warp == 12 && lane == 0) TRACE(12, c);
@@ -819,7 +758,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 }
 
 struct WsLayout {
-  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, total;
+  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, o_f32, total;
   int64_t chunks;
 };
 
@@ -836,11 +775,15 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   L.p_lo = off; off = up(off + recs * REC_P);
   L.u = off; off = up(off + recs * (size_t)U_REC_BYTES);
   L.scal = off; off = up(off + recs * (size_t)(SCAL_FLOATS * 4));
+  L.o_f32 = off;
+  if (a.z != nullptr) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // un-normalised output for the gated norm
   L.total = off;
   return L;
 }
 
 }  // namespace
+
+int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream);
 
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
 
@@ -897,8 +840,26 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
   }
   chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po);
   AVE_CUDA_TRY(cudaGetLastError());
-  chunk_scan_tc_kernel<<<(unsigned)a.n_seqs * (unsigned)a.Hv, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal);
+  float* o_f32 = a.z ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
+  chunk_scan_tc_kernel<<<(unsigned)a.n_seqs * (unsigned)a.Hv, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal, o_f32);
   AVE_CUDA_TRY(cudaGetLastError());
+  if (a.z != nullptr) {  // gated RMSNorm over the fp32 output, one launch per batch row
+    for (int b = 0; b < a.B; ++b) {
+      AveGdnNormArgs nb{};
+      nb.struct_size = sizeof(nb);
+      nb.flags = a.flags & AVE_GDN_FLAG_GATE_FIRST;
+      nb.rows = (int64_t)a.T * a.Hv;
+      nb.d = D; nb.heads = a.Hv; nb.eps = a.norm_eps; nb.weight = a.norm_weight;
+      nb.x = o_f32 + (int64_t)b * a.T * a.Hv * D;
+      nb.x_stride_t = (int64_t)a.Hv * D; nb.x_stride_h = D;
+      nb.z = reinterpret_cast<const __nv_bfloat16*>(a.z) + b * a.z_stride_b;
+      nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
+      nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_stride_b;
+      nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
+      const int rc = launch_gated_rmsnorm_f32in(nb, stream);
+      if (rc != AVE_GDN_OK) return rc;
+    }
+  }
   return AVE_GDN_OK;
 }
 
