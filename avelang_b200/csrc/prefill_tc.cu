@@ -197,7 +197,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   const float bC = bs[C - 1];
   if (tid < C) {
     float* sc = out.scal + rec * SCAL_FLOATS;
-    sc[tid] = __expf(bs[tid]) * qn[tid];             // o_i = scale (qs_i (H q_i) + ...)
+    sc[tid] = __expf(bs[tid]) * qn[tid] * a.scale;   // o_i = qs_i (H q_i) + (scale P Vn)_i: the output scale is folded in here and in P
     sc[C + tid] = __expf(bC - bs[tid]) * kn[tid];    // Vd_j = ks_j Vn_j
     sc[2 * C + tid] = __expf(bC);
   }
@@ -224,7 +224,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       }
     } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
       const int i = r - C;
-      const float bi = bs[i], fi = (i < cr.len) ? qn[i] : 0.f;
+      const float bi = bs[i], fi = (i < cr.len) ? qn[i] * a.scale : 0.f;
       uint32_t ph[16], pl[16];
 #pragma unroll
       for (int w = 0; w < 16; ++w) {
@@ -378,8 +378,9 @@ constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 6
 constexpr int STAGE = 81920;                         // multiple of 1024
 constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
 constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
-constexpr int OFF_SCAL = 2 * STAGE;                  // 2 x [qs | ks | decay]
-constexpr int OFF_U = OFF_SCAL + 2 * SCAL_BYTES;     // fp32 [64][128], single buffer
+constexpr int OFF_SCAL = 2 * STAGE;                  // 4 x [qs | ks | decay]: a deeper ring than the tile stages, because
+                                                     // the output warps read qs up to a chunk after the stage is recycled
+constexpr int OFF_U = OFF_SCAL + 4 * SCAL_BYTES;     // fp32 [64][128], single buffer
 constexpr int U_BYTES = U_REC_BYTES;
 constexpr int OFF_BARS = OFF_U + U_BYTES;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
@@ -482,7 +483,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&full[0], 1); tc::mbar_init(&full[1], 1);
-    tc::mbar_init(&empty[0], 13); tc::mbar_init(&empty[1], 13);
+    tc::mbar_init(&empty[0], 9); tc::mbar_init(&empty[1], 9);
     tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
     tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
     tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 8);
@@ -518,7 +519,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
         tc::tma_load_2d(st + ST_PHI, &maps.p_hi, &full[s], 0, row);
         tc::tma_load_2d(st + ST_PLO, &maps.p_lo, &full[s], 0, row);
-        tc::bulk_load(smem + OFF_SCAL + s * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
+        tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
         // U of chunk c replaces U of chunk c-1 once the chain epilogue has consumed it
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
         tc::mbar_expect_tx(u_full, U_BYTES);
@@ -623,7 +624,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     for (int c = 0; c < n_chunks && alive; ++c) {
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + s * SCAL_BYTES);
+      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
       if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
       if (!tc::mbar_wait(u_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(6, c);
@@ -708,15 +709,18 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     float* of = o_f32 ? o_f32 + ((int64_t)sp.b * a.T * a.Hv + h) * D + d : nullptr;
     bool alive = true;
     for (int c = 0; c < n_chunks && alive; ++c) {
-      const int s = c & 1;
-      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + s * SCAL_BYTES);
+      const uint32_t cp = (uint32_t)c & 1u;
+      const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
       const int len = min(C, sp.len - c * C);
       const int64_t tok0 = sp.t0 + c * C;
-      if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
+      // o_full is committed by the MMA warp after it saw this chunk's stage (tiles and scale vectors) land, so it also
+      // orders the scale vectors; waiting on the stage barrier here would alias phases once this warp lags a chunk
       if (!tc::mbar_wait(o_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 12 && lane == 0) TRACE(11, c);
       tc::tc_fence_after_sync();
+      float* pf = of ? of + tok0 * ((int64_t)a.Hv * D) : nullptr;
+      __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
+      const int64_t fstep = (int64_t)a.Hv * D, bstep = a.o_stride_t;
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t o1[32], o2[32];
@@ -728,22 +732,34 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
         }
+        float ov[32];
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * part + 4 * j4);
-          const float qv[4] = {qs.x, qs.y, qs.z, qs.w};
+          ov[4 * j4 + 0] = fmaf(qs.x, __uint_as_float(o1[4 * j4 + 0]), __uint_as_float(o2[4 * j4 + 0]));
+          ov[4 * j4 + 1] = fmaf(qs.y, __uint_as_float(o1[4 * j4 + 1]), __uint_as_float(o2[4 * j4 + 1]));
+          ov[4 * j4 + 2] = fmaf(qs.z, __uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 2]));
+          ov[4 * j4 + 3] = fmaf(qs.w, __uint_as_float(o1[4 * j4 + 3]), __uint_as_float(o2[4 * j4 + 3]));
+        }
+        const int n_here = min(32, len - 32 * part);  // tokens of this half that exist
+        if (pf != nullptr) {
+          if (n_here == 32) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 4 * j4 + e, i = 32 * part + j;
-            const float ov = a.scale * fmaf(qv[e], __uint_as_float(o1[j]), __uint_as_float(o2[j]));
-            if (i < len) {
-              if (of != nullptr) of[(tok0 + i) * ((int64_t)a.Hv * D)] = ov;
-              else og[(tok0 + i) * a.o_stride_t + d] = __float2bfloat16(ov);
-            }
+            for (int j = 0; j < 32; ++j) { *pf = ov[j]; pf += fstep; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { if (j < n_here) *pf = ov[j]; pf += fstep; }
+          }
+        } else {
+          if (n_here == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { *pb = __float2bfloat16(ov[j]); pb += bstep; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { if (j < n_here) *pb = __float2bfloat16(ov[j]); pb += bstep; }
           }
         }
       }
-      if (lane == 0) tc::mbar_arrive(&empty[s]);
       if (warp == 12 && lane == 0) TRACE(12, c);
     }
   }
