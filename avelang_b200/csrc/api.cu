@@ -8,7 +8,7 @@ thread_local int g_last_cuda_error = 0;
 int launch_decode(const AveGdnArgs& a, cudaStream_t stream);
 int launch_prefill_simt(const AveGdnArgs& a, cudaStream_t stream);
 size_t prefill_simt_workspace_bytes(const AveGdnArgs& a);
-int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream);
+int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream = true);
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a);
 int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream);
 int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);

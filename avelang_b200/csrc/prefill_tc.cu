@@ -30,7 +30,7 @@ struct PrepOut {
   float *u, *scal;
 };
 
-struct ChunkRef { int n, b, t0, len; bool ok; };
+struct ChunkRef { int n, b, t0, len, cis; bool ok; };  // cis: index of the chunk inside its sequence
 
 __device__ __forceinline__ ChunkRef find_chunk(const AveGdnArgs& a, const int32_t* chunk_start, int c) {
   ChunkRef r; r.ok = false;
@@ -38,7 +38,8 @@ __device__ __forceinline__ ChunkRef find_chunk(const AveGdnArgs& a, const int32_
     const int per = (a.T + C - 1) / C;
     r.n = c / per; r.b = r.n;
     if (r.n >= a.B) return r;
-    r.t0 = (c - r.n * per) * C; r.len = min(C, a.T - r.t0); r.ok = true;
+    r.cis = c - r.n * per;
+    r.t0 = r.cis * C; r.len = min(C, a.T - r.t0); r.ok = true;
     return r;
   }
   if (c >= chunk_start[a.n_seqs]) return r;
@@ -46,7 +47,7 @@ __device__ __forceinline__ ChunkRef find_chunk(const AveGdnArgs& a, const int32_
   while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (chunk_start[mid] <= c) lo = mid; else hi = mid; }
   const int s0 = a.cu_seqlens[lo], s1 = a.cu_seqlens[lo + 1];
   if (s0 < 0 || s1 < s0 || s1 > a.T) return r;
-  r.n = lo; r.b = 0; r.t0 = s0 + (c - chunk_start[lo]) * C; r.len = min(C, s1 - r.t0); r.ok = r.len > 0;
+  r.n = lo; r.b = 0; r.cis = c - chunk_start[lo]; r.t0 = s0 + r.cis * C; r.len = min(C, s1 - r.t0); r.ok = r.len > 0;
   return r;
 }
 
@@ -73,6 +74,19 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bflo
   lo = __float2bfloat16(x - __bfloat162float(hi));
 }
 
+#ifdef AVE_TRACE
+__device__ unsigned long long g_tl[64];  // [slot][0] = earliest CTA start, [slot][1] = latest CTA end (globaltimer ns)
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TL_START(slot) do { if (threadIdx.x == 0) atomicMin(&g_tl[2 * (slot)], gtime()); } while (0)
+#define TL_END(slot) do { if (threadIdx.x == 0) atomicMax(&g_tl[2 * (slot) + 1], gtime()); } while (0)
+__device__ long long g_trace[16 * 1024];
+#define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot, c) do {} while (0)
+#define TL_START(slot) do {} while (0)
+#define TL_END(slot) do {} while (0)
+#endif
+
 struct GdnMaps {
   CUtensorMap q, k, v, w_hi, w_lo, p_hi, p_lo;
 };
@@ -96,7 +110,8 @@ constexpr uint32_t PT_GRAM = 0, PT_W = 64, PT_U = 128;  // TMEM columns (256 all
 //   tensor cores: W^T = K^T (T diag(beta e^b))^T,  U^T = V^T (T diag(beta))^T   (M = 128 = d_k / d_v, N = 64 tokens)
 // W^T leaves as bf16 hi + lo [128][64] (the scan reads it as an MN-major B operand), U^T as fp32 [128][68].
 __global__ void __launch_bounds__(PREP_THREADS, 2)
-chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out) {
+chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out,
+                  int seg_c0, int seg_n, int compact_grid) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][64], row i holds A[i][0..i-1], zero elsewhere
@@ -111,10 +126,20 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
-  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int h = blockIdx.y, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  // Whole-batch launches index every chunk of the batch; range launches (seg_n chunks per sequence) use the compact
+  // grid n_seqs x seg_n so that no CTA is spent on chunks outside the range.
+  int c = blockIdx.x;
+  if (compact_grid) {
+    const int n = blockIdx.x / seg_n, cis = seg_c0 + blockIdx.x % seg_n;
+    const int per = a.cu_seqlens ? (chunk_start[n + 1] - chunk_start[n]) : (a.T + C - 1) / C;
+    if (cis >= per) return;
+    c = (a.cu_seqlens ? chunk_start[n] : n * per) + cis;
+  }
   const ChunkRef cr = find_chunk(a, chunk_start, c);
-  if (!cr.ok) return;
+  if (!cr.ok || cr.cis < seg_c0 || cr.cis >= seg_c0 + seg_n) return;  // not in this launch's range of chunks
+  TL_START(compact_grid ? seg_c0 / seg_n : 0);
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
@@ -361,6 +386,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::tmem_dealloc(tm, 256);
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
+  TL_END(compact_grid ? seg_c0 / seg_n : 0);
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
@@ -388,12 +414,6 @@ constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
 constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO = 160, TM_VDHI = 192, TM_VDLO = 224,
                    TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
 
-#ifdef AVE_TRACE
-__device__ long long g_trace[16 * 1024];
-#define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot, c) do {} while (0)
-#endif
 
 __device__ __forceinline__ uint32_t pack_hi(float x0, float x1) { return pack_bf16x2(x0, x1); }
 __device__ __forceinline__ uint32_t pack_lo(float x0, float x1, uint32_t hi_packed) {
@@ -425,7 +445,8 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
-                     const float* __restrict__ u_ws, const float* __restrict__ scal_ws, float* __restrict__ o_f32) {
+                     const float* __restrict__ u_ws, const float* __restrict__ scal_ws, float* __restrict__ o_f32,
+                     float* __restrict__ carry, int seg_c0, int seg_n) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const float* u_s = reinterpret_cast<const float*>(smem + OFF_U);
@@ -448,8 +469,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x / a.Hv, h = blockIdx.x % a.Hv;
   const int hk = h / (a.Hv / a.Hk);
-  const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
+  SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
+  if (seg_c0 > 0 && sp.ok && sp.len > 0 && seg_c0 * C >= sp.len) return;  // finished in an earlier launch
   if (!sp.ok || sp.len == 0) {
+    if (seg_c0 > 0) return;
     // zero-length sequence: the final state is the initial state
     if (sp.ok && a.final_state != nullptr && a.final_state != a.initial_state) {
       const int slot0 = a.state_indices ? a.state_indices[n] : n;
@@ -478,8 +501,15 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
     return;
   }
+  // A launch covers chunks [seg_c0, seg_c0 + seg_n) of every sequence: from here on the sequence is narrowed to that
+  // range, and the state enters from / leaves to the carry buffer unless this is the sequence's first / last range.
+  const bool seg_first = seg_c0 == 0;
+  const bool seg_last = (seg_c0 + seg_n) * C >= sp.len;
+  const int c_first = (a.cu_seqlens ? chunk_start[n] : n * ((a.T + C - 1) / C)) + seg_c0;
+  sp.t0 += seg_c0 * C;
+  sp.len = min(sp.len - seg_c0 * C, seg_n * C);
   const int n_chunks = (sp.len + C - 1) / C;
-  const int c_first = a.cu_seqlens ? chunk_start[n] : n * ((a.T + C - 1) / C);
+  const int64_t carry_tile = ((int64_t)n * a.Hv + h) * (int64_t)(D * D);
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&full[0], 1); tc::mbar_init(&full[1], 1);
@@ -496,6 +526,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
+  TL_START(8 + (seg_n < (1 << 20) ? seg_c0 / seg_n : 0));
 
   if (warp < 4) {
   tc::reg_set<REGS_CTRL, 128>();
@@ -595,9 +626,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     uint32_t sync_phase = 0;
 
     float Hreg[64];  // H[d][64*grp + i] = M[64*grp + i][d]
-    if (a.initial_state != nullptr) {
+    const float* state_in = seg_first ? (a.initial_state ? a.initial_state + tile : nullptr) : carry + carry_tile;
+    float* state_out = seg_last ? (a.final_state ? a.final_state + tile : nullptr) : carry + carry_tile;
+    if (state_in != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) Hreg[i] = a.initial_state[tile + (int64_t)(64 * grp + i) * D + d];
+      for (int i = 0; i < 64; ++i) Hreg[i] = state_in[(int64_t)(64 * grp + i) * D + d];
     } else {
 #pragma unroll
       for (int i = 0; i < 64; ++i) Hreg[i] = 0.f;
@@ -694,9 +727,9 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       if (lane == 0) tc::mbar_arrive(&empty[s]);  // this warp no longer reads the stage's scale vectors
       if (warp == 4 && lane == 0) TRACE(10, c);
     }
-    if (alive && a.final_state != nullptr) {
+    if (alive && state_out != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) a.final_state[tile + (int64_t)(64 * grp + i) * D + d] = Hreg[i];
+      for (int i = 0; i < 64; ++i) state_out[(int64_t)(64 * grp + i) * D + d] = Hreg[i];
     }
   } else {
     tc::reg_set<REGS_OUT, 128>();
@@ -771,11 +804,13 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 512);
   }
+  TL_END(8 + (seg_n < (1 << 20) ? seg_c0 / seg_n : 0));
 }
 
 struct WsLayout {
-  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, o_f32, total;
+  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, o_f32, carry, total;
   int64_t chunks;
+  int segments, seg_chunks;  // chunk ranges per sequence handled by separate launches
 };
 
 WsLayout ws_layout(const AveGdnArgs& a) {
@@ -793,6 +828,13 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   L.scal = off; off = up(off + recs * (size_t)(SCAL_FLOATS * 4));
   L.o_f32 = off;
   if (a.z != nullptr) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // un-normalised output for the gated norm
+  // Few long chains (fewer scan CTAs than half the SMs): cut the sequences into ranges so that pass 1 of range i+1 runs
+  // on the idle SMs while pass 2 of range i walks its chain.  The state crosses ranges through the carry buffer.
+  const int max_chunks = (a.T + C - 1) / C;
+  L.segments = ((int64_t)a.n_seqs * a.Hv <= 74 && max_chunks >= 32) ? 4 : 1;
+  L.seg_chunks = (max_chunks + L.segments - 1) / L.segments;
+  L.carry = off;
+  if (L.segments > 1) off = up(off + (size_t)a.n_seqs * a.Hv * D * D * 4);
   L.total = off;
   return L;
 }
@@ -804,12 +846,42 @@ int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream);
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
 
 #ifdef AVE_TRACE
+extern "C" int ave_tl_reset(void) {
+  unsigned long long init[64];
+  for (int i = 0; i < 32; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0; }
+  return (int)cudaMemcpyToSymbol(g_tl, init, sizeof(init));
+}
+extern "C" int ave_tl_read(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_tl, sizeof(unsigned long long) * 64); }
 extern "C" int ave_trace_read(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
 }
 #endif
 
-int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
+// Helper streams and events for the range-overlapped schedule, one set per device, created on first use.  Pass 2
+// runs on a high-priority stream so that, when a range's pass 1 completes and both its pass 2 and the next range's
+// pass 1 become runnable on an empty GPU, the few whole-SM pass-2 CTAs are placed first.
+struct SideStream {
+  cudaStream_t prep = nullptr, scan = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  cudaEvent_t done[4] = {};
+};
+static SideStream* side_stream(int dev) {
+  static SideStream per_dev[64];
+  SideStream& s = per_dev[dev & 63];
+  if (s.prep == nullptr) {
+    int lo = 0, hi = 0;
+    if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithPriority(&s.prep, cudaStreamNonBlocking, lo) != cudaSuccess) { s.prep = nullptr; return nullptr; }
+    bool ok = cudaStreamCreateWithPriority(&s.scan, cudaStreamNonBlocking, hi) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 4; ++i) ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) return nullptr;
+  }
+  return &s;
+}
+
+int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream) {
   const WsLayout L = ws_layout(a);
   if (L.chunks == 0 || a.n_seqs == 0) return AVE_GDN_OK;
   char* ws = reinterpret_cast<char*>(a.workspace);
@@ -854,11 +926,36 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream) {
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
     attr_set_dev[dev & 63] = true;
   }
-  chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po);
-  AVE_CUDA_TRY(cudaGetLastError());
   float* o_f32 = a.z ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
-  chunk_scan_tc_kernel<<<(unsigned)a.n_seqs * (unsigned)a.Hv, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal, o_f32);
-  AVE_CUDA_TRY(cudaGetLastError());
+  float* carry = reinterpret_cast<float*>(ws + L.carry);
+  const dim3 prep_grid((unsigned)L.chunks, (unsigned)a.Hv);
+  const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)a.Hv;
+  SideStream* side = (L.segments > 1 && allow_side_stream) ? side_stream(dev) : nullptr;
+  if (side == nullptr) {
+    const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
+    chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
+    AVE_CUDA_TRY(cudaGetLastError());
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry, 0, big);
+    AVE_CUDA_TRY(cudaGetLastError());
+  } else {
+    // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on the other once pass 1 of range i is
+    // done; both fork from the caller's stream and join back into it through events
+    AVE_CUDA_TRY(cudaEventRecord(side->fork, stream));
+    AVE_CUDA_TRY(cudaStreamWaitEvent(side->prep, side->fork, 0));
+    AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->fork, 0));
+    for (int i = 0; i < L.segments; ++i) {
+      chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * L.seg_chunks), (unsigned)a.Hv), PREP_THREADS, smem_prep, side->prep>>>(
+          a, maps, chunk_start, po, i * L.seg_chunks, L.seg_chunks, 1);
+      AVE_CUDA_TRY(cudaGetLastError());
+      AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
+      AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry,
+                                                                            i * L.seg_chunks, L.seg_chunks);
+      AVE_CUDA_TRY(cudaGetLastError());
+    }
+    AVE_CUDA_TRY(cudaEventRecord(side->join, side->scan));
+    AVE_CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
+  }
   if (a.z != nullptr) {  // gated RMSNorm over the fp32 output, one launch per batch row
     for (int b = 0; b < a.B; ++b) {
       AveGdnNormArgs nb{};
@@ -915,5 +1012,6 @@ extern "C" int ave_gdn_chunk_prefill_noalloc(const AveGdnArgs* args, void* strea
   local.workspace = scratch_of_device[dev];
   local.workspace_bytes = kStaticScratchBytes;
   // every scratch record a launch reads is written earlier in the same launch sequence, so nothing needs clearing
-  return launch_prefill_tc(local, reinterpret_cast<cudaStream_t>(stream));
+  // single-stream schedule: this variant creates no streams or events either
+  return launch_prefill_tc(local, reinterpret_cast<cudaStream_t>(stream), false);
 }
