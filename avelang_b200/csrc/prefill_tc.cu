@@ -96,11 +96,66 @@ struct GdnMaps {
 // 64-wide halves, [K_h0 | Q_h0 | K_h1 | Q_h1], so that one M = 128 MMA reads [K; Q] as its A operand (rows 0..63 =
 // K, 64..127 = Q) and the K rows alone as its N = 64 B operand: lanes 0..63 of the accumulator are K K^T, lanes
 // 64..127 are Q K^T.
+
+// ---- 16x16 fp32 block algebra on legacy warp MMAs (m16n8k8 tf32), used for the triangular inverse -----------------
+// Blocks live in shared memory as [16][BLK_LD] fp32.  Each product is issued as three tf32 MMAs per fragment
+// (hi*hi + lo*hi + hi*lo) so the result carries fp32-level accuracy.
+constexpr int BLK_LD = 20;                 // row stride (floats): conflict-free left-operand fragment loads
+constexpr int BLK_FLOATS = 16 * BLK_LD;    // 320
+__host__ __device__ constexpr int tri(int r, int c) { return r * (r + 1) / 2 + c; }  // lower-triangular block index
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// acc[nt] (+)= L * R for one 16x16 block pair; `lget(row, col)` returns element (row, col) of the left operand.
+template <class LGet>
+__device__ __forceinline__ void block_mma(float (&acc)[2][4], LGet lget, const float* __restrict__ R, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks) {
+    const float af[4] = {lget(g, 8 * ks + t), lget(g + 8, 8 * ks + t), lget(g, 8 * ks + t + 4), lget(g + 8, 8 * ks + t + 4)};
+    uint32_t ah[4], al[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { ah[e] = to_tf32(af[e]); al[e] = to_tf32(af[e] - __uint_as_float(ah[e])); }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float bf[2] = {R[(8 * ks + t) * BLK_LD + 8 * nt + g], R[(8 * ks + t + 4) * BLK_LD + 8 * nt + g]};
+      uint32_t bh[2], bl[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) { bh[e] = to_tf32(bf[e]); bl[e] = to_tf32(bf[e] - __uint_as_float(bh[e])); }
+      mma_tf32(acc[nt], ah, bh);
+      mma_tf32(acc[nt], al, bh);
+      mma_tf32(acc[nt], ah, bl);
+    }
+  }
+}
+// accumulator fragment -> block in shared memory (optionally negated)
+__device__ __forceinline__ void block_store(float* __restrict__ dst, const float (&acc)[2][4], int lane, float sign = 1.f) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    *reinterpret_cast<float2*>(dst + g * BLK_LD + 8 * nt + 2 * t) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+    *reinterpret_cast<float2*>(dst + (g + 8) * BLK_LD + 8 * nt + 2 * t) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+  }
+}
+
 constexpr int PREP_THREADS = 256;
 constexpr int U_LD = 68;                              // row stride (floats) of U^T: 16-byte rows, conflict-free float4 reads
 constexpr int U_REC_BYTES = D * U_LD * 4;             // 34816
 constexpr int PP_KQ = 0, PP_V = 32768, PP_T = 49152,  // PP_T: Tw_hi | Tw_lo | Tu_hi | Tu_lo, bf16 [64][64] K-major tiles
-              PP_A = PP_T + 4 * 8192, PP_SC = PP_A + C * C * 4, PP_BARS = PP_SC + 4 * C * 4;
+              PP_A = PP_T + 4 * 8192,                 // A, later T: 10 lower-triangular 16x16 fp32 blocks
+              PP_DI = PP_A + 10 * BLK_FLOATS * 4,     // inverses of the 4 diagonal blocks
+              PP_SC = PP_DI + 4 * BLK_FLOATS * 4, PP_BARS = PP_SC + 4 * C * 4;
+// E (6 blocks), E^2 (3) and E^3 (1) are dead before the operand tiles are written, so they borrow the tile region
+constexpr int PP_E = PP_T, PP_E2 = PP_E + 6 * BLK_FLOATS * 4, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
+static_assert(PP_E3 + BLK_FLOATS * 4 <= PP_T + 4 * 8192, "block scratch must fit inside the tile region");
 constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
 constexpr uint32_t PT_GRAM = 0, PT_W = 64, PT_U = 128;  // TMEM columns (256 allocated)
 
@@ -114,7 +169,11 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
                   int seg_c0, int seg_n, int compact_grid) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* As = reinterpret_cast<float*>(smem + PP_A);   // [64][64], row i holds A[i][0..i-1], zero elsewhere
+  float* Ab = reinterpret_cast<float*>(smem + PP_A);   // A as 16x16 blocks (r >= c), block tri(r,c); later T
+  float* Di = reinterpret_cast<float*>(smem + PP_DI);  // (I + A_rr)^-1
+  float* Eb = reinterpret_cast<float*>(smem + PP_E);
+  float* E2b = reinterpret_cast<float*>(smem + PP_E2);
+  float* E3b = reinterpret_cast<float*>(smem + PP_E3);
   float* bs = reinterpret_cast<float*>(smem + PP_SC);
   float* betas = bs + C;
   float* qn = betas + C;
@@ -245,7 +304,10 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
           const int j = 32 * colhalf + 4 * j4 + e;
           av[e] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[4 * j4 + e]) : 0.f;
         }
-        *reinterpret_cast<float4*>(As + i * C + 32 * colhalf + 4 * j4) = make_float4(av[0], av[1], av[2], av[3]);
+        const int jb = (32 * colhalf + 4 * j4) >> 4;  // column block; blocks above the diagonal are not stored
+        if (jb <= (i >> 4))
+          *reinterpret_cast<float4*>(Ab + tri(i >> 4, jb) * BLK_FLOATS + (i & 15) * BLK_LD + ((32 * colhalf + 4 * j4) & 15)) =
+              make_float4(av[0], av[1], av[2], av[3]);
       }
     } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
       const int i = r - C;
@@ -269,43 +331,104 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     }
   }
   __syncthreads();
-  // T = (I + A)^-1, column col, rows 4m + part kept in x[m].  x starts at zero and T is lower triangular, so the
-  // row-i sum needs no bounds: terms with j < col or j >= i multiply zeros.
-  {
-    const int col = tid >> 2, part = tid & 3;
-    const int first_row = (col & ~7);  // rows above the warp's first column are identically zero
+  // ---- T = (I + A)^-1 by 16x16 blocks.  With D = blockdiag(I + A_rr) and E = D^-1 (A - A_D) (strictly block lower,
+  // E^4 = 0):  T = (I - E + E^2 - E^3) D^-1.  Only the four small D_r^-1 need a sequential substitution.
+  if (tid < 64) {  // column k of (I + A_rr)^-1, 16 rows, one thread each
+    const int r = tid >> 4, k = tid & 15;
+    const float* Arr = Ab + tri(r, r) * BLK_FLOATS;
     float x[16];
 #pragma unroll
-    for (int m = 0; m < 16; ++m) x[m] = 0.f;
+    for (int i = 0; i < 16; ++i) {
+      float s0 = (i == k) ? 1.f : 0.f, s1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < C; ++i) {
-      if (i >= first_row) {
-        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-        for (int m = 0; m < (i + 3) / 4; ++m) {
-          const float av = As[i * C + 4 * m + part];
-          if (m & 1) s1 = fmaf(av, x[m], s1); else s0 = fmaf(av, x[m], s0);
-        }
-        float tot = s0 + s1;
-        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-        const float ti = ((i == col) ? 1.f : 0.f) - tot;
-        if (part == (i & 3)) x[i >> 2] = ti;
+      for (int j = 0; j < i; ++j) {
+        const float av = Arr[i * BLK_LD + j];
+        if (j & 1) s1 = fmaf(-av, x[j], s1); else s0 = fmaf(-av, x[j], s0);
       }
+      x[i] = s0 + s1;
     }
-    // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j = col], 128-byte swizzle
-    const float fu = betas[col], fw = fu * __expf(bs[col]) * kn[col];
 #pragma unroll
-    for (int m = 0; m < 16; ++m) {
-      const int i = 4 * m + part;
-      const uint32_t off = (uint32_t)(i * 128 + ((((col >> 3) ^ (i & 7))) << 4) + (col & 7) * 2);
-      __nv_bfloat16 hi, lo;
-      split_bf16(x[m] * fw, hi, lo);
-      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 8192 + off) = lo;
-      split_bf16(x[m] * fu, hi, lo);
-      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 16384 + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(smem + PP_T + 24576 + off) = lo;
+    for (int i = 0; i < 16; ++i) Di[r * BLK_FLOATS + i * BLK_LD + k] = x[i];
+  }
+  __syncthreads();
+  // E_rc = D_r^-1 A_rc, r > c: six products, one warp each
+  if (warp < 6) {
+    constexpr int RR[6] = {1, 2, 2, 3, 3, 3}, CC[6] = {0, 0, 1, 0, 1, 2};
+    const int r = RR[warp], c = CC[warp];
+    float acc[2][4] = {};
+    const float* L = Di + r * BLK_FLOATS;
+    block_mma(acc, [&](int row, int col) { return L[row * BLK_LD + col]; }, Ab + tri(r, c) * BLK_FLOATS, lane);
+    block_store(Eb + (tri(r, c) - r) * BLK_FLOATS, acc, lane);  // strictly-lower block index: tri(r,c) - r
+  }
+  __syncthreads();
+  // E^2: (2,0) = E21 E10, (3,1) = E32 E21, (3,0) = E31 E10 + E32 E20
+  auto Eblk = [&](int r, int c) { return Eb + (tri(r, c) - r) * BLK_FLOATS; };
+  if (warp < 3) {
+    float acc[2][4] = {};
+    if (warp == 0) {
+      const float* L = Eblk(2, 1);
+      block_mma(acc, [&](int row, int col) { return L[row * BLK_LD + col]; }, Eblk(1, 0), lane);
+    } else if (warp == 1) {
+      const float* L = Eblk(3, 2);
+      block_mma(acc, [&](int row, int col) { return L[row * BLK_LD + col]; }, Eblk(2, 1), lane);
+    } else {
+      const float* L1 = Eblk(3, 1);
+      block_mma(acc, [&](int row, int col) { return L1[row * BLK_LD + col]; }, Eblk(1, 0), lane);
+      const float* L2 = Eblk(3, 2);
+      block_mma(acc, [&](int row, int col) { return L2[row * BLK_LD + col]; }, Eblk(2, 0), lane);
+    }
+    block_store(E2b + warp * BLK_FLOATS, acc, lane);  // order: (2,0), (3,1), (3,0)
+  }
+  __syncthreads();
+  // E^3: (3,0) = E32 E2_20
+  if (warp == 0) {
+    float acc[2][4] = {};
+    const float* L = Eblk(3, 2);
+    block_mma(acc, [&](int row, int col) { return L[row * BLK_LD + col]; }, E2b, lane);
+    block_store(E3b, acc, lane);
+  }
+  __syncthreads();
+  // T_rc = (-E + E^2 - E^3)_rc D_c^-1, r > c (written over A_rc, which is no longer needed); T_rr = D_r^-1
+  if (warp < 6) {
+    constexpr int RR[6] = {1, 2, 2, 3, 3, 3}, CC[6] = {0, 0, 1, 0, 1, 2};
+    const int r = RR[warp], c = CC[warp];
+    const float* e1 = Eblk(r, c);
+    const float* e2 = (r - c >= 2) ? E2b + ((r == 2) ? 0 : (c == 1 ? 1 : 2)) * BLK_FLOATS : nullptr;
+    const float* e3 = (r - c == 3) ? E3b : nullptr;
+    float acc[2][4] = {};
+    block_mma(acc, [&](int row, int col) {
+      float v = -e1[row * BLK_LD + col];
+      if (e2 != nullptr) v += e2[row * BLK_LD + col];
+      if (e3 != nullptr) v -= e3[row * BLK_LD + col];
+      return v;
+    }, Di + c * BLK_FLOATS, lane);
+    block_store(Ab + tri(r, c) * BLK_FLOATS, acc, lane);
+  }
+  __syncthreads();
+  // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j], 128-byte swizzle, two columns per store
+  {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int pidx = tid + PREP_THREADS * q;
+      const int i = pidx >> 5, j = (pidx & 31) * 2;
+      float t0 = 0.f, t1 = 0.f;
+      if (j <= i) {
+        const int rb = i >> 4, cb = j >> 4;
+        const float* src = (rb == cb) ? Di + rb * BLK_FLOATS : Ab + tri(rb, cb) * BLK_FLOATS;
+        const float2 tv = *reinterpret_cast<const float2*>(src + (i & 15) * BLK_LD + (j & 15));
+        t0 = tv.x; t1 = (j + 1 <= i) ? tv.y : 0.f;
+      }
+      const float fu0 = betas[j], fu1 = betas[j + 1];
+      const float fw0 = fu0 * __expf(bs[j]) * kn[j], fw1 = fu1 * __expf(bs[j + 1]) * kn[j + 1];
+      const uint32_t off = (uint32_t)(i * 128 + ((((j >> 3) ^ (i & 7))) << 4) + (j & 7) * 2);
+      const float w0 = t0 * fw0, w1 = t1 * fw1, u0 = t0 * fu0, u1 = t1 * fu1;
+      const uint32_t wh = pack_bf16x2(w0, w1), uh = pack_bf16x2(u0, u1);
+      *reinterpret_cast<uint32_t*>(smem + PP_T + off) = wh;
+      *reinterpret_cast<uint32_t*>(smem + PP_T + 8192 + off) =
+          pack_bf16x2(w0 - __uint_as_float(wh << 16), w1 - __uint_as_float(wh & 0xffff0000u));
+      *reinterpret_cast<uint32_t*>(smem + PP_T + 16384 + off) = uh;
+      *reinterpret_cast<uint32_t*>(smem + PP_T + 24576 + off) =
+          pack_bf16x2(u0 - __uint_as_float(uh << 16), u1 - __uint_as_float(uh & 0xffff0000u));
     }
   }
   tc::fence_proxy_async_smem();
