@@ -80,11 +80,13 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define TL_START(slot) do { if (threadIdx.x == 0) atomicMin(&g_tl[2 * (slot)], gtime()); } while (0)
 #define TL_END(slot) do { if (threadIdx.x == 0) atomicMax(&g_tl[2 * (slot) + 1], gtime()); } while (0)
 __device__ long long g_trace[16 * 1024];
+#define PTRACE(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[16 * 1000 + (slot)] = clock64(); } while (0)
 #define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(slot, c) do {} while (0)
 #define TL_START(slot) do {} while (0)
 #define TL_END(slot) do {} while (0)
+#define PTRACE(slot) do {} while (0)
 #endif
 
 struct GdnMaps {
@@ -118,6 +120,7 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 template <class LGet>
 __device__ __forceinline__ void block_mma(float (&acc)[2][4], LGet lget, const float* __restrict__ R, int lane) {
   const int g = lane >> 2, t = lane & 3;
+  float lh[2][4] = {}, hl[2][4] = {};  // separate chains for the lo*hi and hi*lo terms: shorter dependent MMA chains
 #pragma unroll
   for (int ks = 0; ks < 2; ++ks) {
     const float af[4] = {lget(g, 8 * ks + t), lget(g + 8, 8 * ks + t), lget(g, 8 * ks + t + 4), lget(g + 8, 8 * ks + t + 4)};
@@ -131,10 +134,14 @@ __device__ __forceinline__ void block_mma(float (&acc)[2][4], LGet lget, const f
 #pragma unroll
       for (int e = 0; e < 2; ++e) { bh[e] = to_tf32(bf[e]); bl[e] = to_tf32(bf[e] - __uint_as_float(bh[e])); }
       mma_tf32(acc[nt], ah, bh);
-      mma_tf32(acc[nt], al, bh);
-      mma_tf32(acc[nt], ah, bl);
+      mma_tf32(lh[nt], al, bh);
+      mma_tf32(hl[nt], ah, bl);
     }
   }
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] += lh[nt][e] + hl[nt][e];
 }
 // accumulator fragment -> block in shared memory (optionally negated)
 __device__ __forceinline__ void block_store(float* __restrict__ dst, const float (&acc)[2][4], int lane, float sign = 1.f) {
@@ -202,6 +209,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
+  PTRACE(0);
   if (tid == 0) {
     tc::mbar_init(tma_bar, 1);
     tc::mbar_init(mma_bar, 1);
@@ -216,7 +224,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_V + 8192, &maps.v, tma_bar, 64, h, cr.t0, cr.b);
   }
-  if (warp == 0) tc::tmem_alloc(tmem_slot, 256);
+  if (warp == 2) tc::tmem_alloc(tmem_slot, 256);
   if (tid < C) {
     const bool valid = tid < cr.len;
     const int64_t off = cr.b * a.g_stride_b + (int64_t)(cr.t0 + tid) * a.g_stride_t + h;
@@ -238,7 +246,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     bs[lane] = v0; bs[32 + lane] = v1;
   }
 
+  PTRACE(1);
   bool ok = tc::mbar_wait(tma_bar, 0, abort_flag);
+  PTRACE(2);
   if (warp == 0) {
     tc::tc_fence_after_sync();
     const bool leader = tc::elect_one();
@@ -279,13 +289,16 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   } else if (tid < C) { kn[tid] = 1.f; qn[tid] = 1.f; }
   __syncthreads();
   const float bC = bs[C - 1];
+  float* fwv = qn;  // q's norm is consumed below; afterwards the slot holds beta_j e^{b_j} kn_j, the column factor of Tw
   if (tid < C) {
     float* sc = out.scal + rec * SCAL_FLOATS;
     sc[tid] = __expf(bs[tid]) * qn[tid] * a.scale;   // o_i = qs_i (H q_i) + (scale P Vn)_i: the output scale is folded in here and in P
     sc[C + tid] = __expf(bC - bs[tid]) * kn[tid];    // Vd_j = ks_j Vn_j
     sc[2 * C + tid] = __expf(bC);
   }
+  PTRACE(3);
   ok = ok && tc::mbar_wait(mma_bar, 0, abort_flag);
+  PTRACE(4);
   tc::tc_fence_after_sync();
   {
     const int quarter = warp & 3, colhalf = warp >> 2;
@@ -331,6 +344,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     }
   }
   __syncthreads();
+  PTRACE(5);
   // ---- T = (I + A)^-1 by 16x16 blocks.  With D = blockdiag(I + A_rr) and E = D^-1 (A - A_D) (strictly block lower,
   // E^4 = 0):  T = (I - E + E^2 - E^3) D^-1.  Only the four small D_r^-1 need a sequential substitution.
   if (tid < 64) {  // column k of (I + A_rr)^-1, 16 rows, one thread each
@@ -349,8 +363,12 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) Di[r * BLK_FLOATS + i * BLK_LD + k] = x[i];
+  } else if (tid < 128) {  // q's norms are no longer read: reuse their slot for the column factors of Tw
+    const int j = tid - 64;
+    fwv[j] = betas[j] * __expf(bs[j]) * kn[j];
   }
   __syncthreads();
+  PTRACE(6);
   // E_rc = D_r^-1 A_rc, r > c: six products, one warp each
   if (warp < 6) {
     constexpr int RR[6] = {1, 2, 2, 3, 3, 3}, CC[6] = {0, 0, 1, 0, 1, 2};
@@ -405,6 +423,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     block_store(Ab + tri(r, c) * BLK_FLOATS, acc, lane);
   }
   __syncthreads();
+  PTRACE(7);
   // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j], 128-byte swizzle, two columns per store
   {
 #pragma unroll
@@ -419,7 +438,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
         t0 = tv.x; t1 = (j + 1 <= i) ? tv.y : 0.f;
       }
       const float fu0 = betas[j], fu1 = betas[j + 1];
-      const float fw0 = fu0 * __expf(bs[j]) * kn[j], fw1 = fu1 * __expf(bs[j + 1]) * kn[j + 1];
+      const float fw0 = fwv[j], fw1 = fwv[j + 1];
       const uint32_t off = (uint32_t)(i * 128 + ((((j >> 3) ^ (i & 7))) << 4) + (j & 7) * 2);
       const float w0 = t0 * fw0, w1 = t1 * fw1, u0 = t0 * fu0, u1 = t1 * fu1;
       const uint32_t wh = pack_bf16x2(w0, w1), uh = pack_bf16x2(u0, u1);
@@ -459,56 +478,81 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     }
     __syncwarp();
   }
+  PTRACE(8);
   ok = ok && tc::mbar_wait(mma2_bar, 0, abort_flag);
+  PTRACE(9);
   tc::tc_fence_after_sync();
   {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // d_k index (warps 0..3) or d_v index (warps 4..7)
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
+    // Each lane owns one output row.  A direct store would scatter 32 rows per instruction, so rows are transposed
+    // through a per-warp staging area (the K/Q/V tiles are dead by now) with an XOR swizzle on 16-byte pieces and
+    // written back as fully coalesced 512-byte stores.
     if (warp < 4) {
-      uint4* wh = reinterpret_cast<uint4*>(out.w_hi + rec * (C * D) + r * C);
-      uint4* wl = reinterpret_cast<uint4*>(out.w_lo + rec * (C * D) + r * C);
+      uint4* st = reinterpret_cast<uint4*>(smem + PP_KQ + warp * 4096);        // 32 rows x 128 B
+      uint4* gh = reinterpret_cast<uint4*>(out.w_hi + rec * (C * D) + (quarter * 32) * C);
+      uint4* gl = reinterpret_cast<uint4*>(out.w_lo + rec * (C * D) + (quarter * 32) * C);
+      uint32_t hi[32], lo[32];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t acc[32];
         tc::tmem_ld32(lane_addr + PT_W + 32 * half, acc);
         tc::tmem_ld_wait();
-        uint32_t hi[16], lo[16];
 #pragma unroll
         for (int w = 0; w < 16; ++w) {
           const float v0 = __uint_as_float(acc[2 * w]), v1 = __uint_as_float(acc[2 * w + 1]);
-          hi[w] = pack_bf16x2(v0, v1);
-          lo[w] = pack_bf16x2(v0 - __uint_as_float(hi[w] << 16), v1 - __uint_as_float(hi[w] & 0xffff0000u));
-        }
-        if (ok) {
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            wh[4 * half + v4] = make_uint4(hi[4 * v4], hi[4 * v4 + 1], hi[4 * v4 + 2], hi[4 * v4 + 3]);
-            wl[4 * half + v4] = make_uint4(lo[4 * v4], lo[4 * v4 + 1], lo[4 * v4 + 2], lo[4 * v4 + 3]);
-          }
+          hi[16 * half + w] = pack_bf16x2(v0, v1);
+          lo[16 * half + w] = pack_bf16x2(v0 - __uint_as_float(hi[16 * half + w] << 16), v1 - __uint_as_float(hi[16 * half + w] & 0xffff0000u));
         }
       }
+      PTRACE(11);
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const uint32_t* src = pass ? lo : hi;
+#pragma unroll
+        for (int p8 = 0; p8 < 8; ++p8) st[lane * 8 + (p8 ^ (lane & 7))] = make_uint4(src[4 * p8], src[4 * p8 + 1], src[4 * p8 + 2], src[4 * p8 + 3]);
+        __syncwarp();
+        if (ok) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int m = 32 * k + lane, row = m >> 3, piece = m & 7;
+            (pass ? gl : gh)[m] = st[row * 8 + (piece ^ (row & 7))];
+          }
+        }
+        __syncwarp();
+      }
+      PTRACE(12);
     } else {
-      uint4* up = reinterpret_cast<uint4*>(out.u + rec * (D * U_LD) + r * U_LD);
+      uint4* st = reinterpret_cast<uint4*>(smem + PP_KQ + 16384 + (warp - 4) * 8192);  // 32 rows x 256 B
+      float* gu = out.u + rec * (D * U_LD) + (quarter * 32) * U_LD;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t acc[32];
         tc::tmem_ld32(lane_addr + PT_U + 32 * half, acc);
         tc::tmem_ld_wait();
-        if (ok) {
 #pragma unroll
-          for (int v4 = 0; v4 < 8; ++v4) up[8 * half + v4] = make_uint4(acc[4 * v4], acc[4 * v4 + 1], acc[4 * v4 + 2], acc[4 * v4 + 3]);
+        for (int p8 = 0; p8 < 8; ++p8)
+          st[lane * 16 + ((8 * half + p8) ^ (lane & 7))] = make_uint4(acc[4 * p8], acc[4 * p8 + 1], acc[4 * p8 + 2], acc[4 * p8 + 3]);
+      }
+      __syncwarp();
+      if (ok) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const int m = 32 * k + lane, row = m >> 4, piece = m & 15;
+          *reinterpret_cast<uint4*>(gu + row * U_LD + piece * 4) = st[row * 16 + (piece ^ (row & 7))];
         }
       }
     }
   }
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 2) {
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 256);
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
+  PTRACE(10);
   TL_END(compact_grid ? seg_c0 / seg_n : 0);
 }
 
