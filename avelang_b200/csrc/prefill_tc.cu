@@ -43,15 +43,15 @@ __device__ __forceinline__ ChunkRef find_chunk(const AveGdnArgs& a, const int32_
     return r;
   }
   if (c >= chunk_start[a.n_seqs]) return r;
-  int lo = 0, hi = a.n_seqs;
-  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (chunk_start[mid] <= c) lo = mid; else hi = mid; }
+  const int lo = chunk_start[a.n_seqs + 1 + c];  // chunk -> sequence map, stored behind the prefix table
   const int s0 = a.cu_seqlens[lo], s1 = a.cu_seqlens[lo + 1];
   if (s0 < 0 || s1 < s0 || s1 > a.T) return r;
   r.n = lo; r.b = 0; r.cis = c - chunk_start[lo]; r.t0 = s0 + r.cis * C; r.len = min(C, s1 - r.t0); r.ok = r.len > 0;
   return r;
 }
 
-__global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int32_t* __restrict__ chunk_start) {
+__global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int32_t* __restrict__ chunk_start,
+                                      int max_chunks) {
   __shared__ int part[1024];
   const int per = (n_seqs + 1023) / 1024;
   const int lo = threadIdx.x * per, hi = min(lo + per, n_seqs);
@@ -66,7 +66,13 @@ __global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, in
   }
   __syncthreads();
   int run = part[threadIdx.x];
-  for (int n = lo; n < hi; ++n) { chunk_start[n] = run; run += max(0, (cu_seqlens[n + 1] - cu_seqlens[n] + C - 1) / C); }
+  int32_t* chunk_seq = chunk_start + n_seqs + 1;  // chunk_seq[c] = sequence that owns chunk c
+  for (int n = lo; n < hi; ++n) {
+    chunk_start[n] = run;
+    const int cnt = max(0, (cu_seqlens[n + 1] - cu_seqlens[n] + C - 1) / C);
+    for (int i = 0; i < cnt && run + i < max_chunks; ++i) chunk_seq[run + i] = n;
+    run += cnt;
+  }
 }
 
 __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
@@ -426,19 +432,19 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   PTRACE(7);
   // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j], 128-byte swizzle, two columns per store
   {
+    const int j = (tid & 31) * 2;  // this thread's column pair; rows (tid >> 5) + 8 q
+    const float fu0 = betas[j], fu1 = betas[j + 1], fw0 = fwv[j], fw1 = fwv[j + 1];
+    const int cb = j >> 4;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      const int pidx = tid + PREP_THREADS * q;
-      const int i = pidx >> 5, j = (pidx & 31) * 2;
+      const int i = (tid >> 5) + 8 * q;
       float t0 = 0.f, t1 = 0.f;
       if (j <= i) {
-        const int rb = i >> 4, cb = j >> 4;
+        const int rb = i >> 4;
         const float* src = (rb == cb) ? Di + rb * BLK_FLOATS : Ab + tri(rb, cb) * BLK_FLOATS;
         const float2 tv = *reinterpret_cast<const float2*>(src + (i & 15) * BLK_LD + (j & 15));
         t0 = tv.x; t1 = (j + 1 <= i) ? tv.y : 0.f;
       }
-      const float fu0 = betas[j], fu1 = betas[j + 1];
-      const float fw0 = fwv[j], fw1 = fwv[j + 1];
       const uint32_t off = (uint32_t)(i * 128 + ((((j >> 3) ^ (i & 7))) << 4) + (j & 7) * 2);
       const float w0 = t0 * fw0, w1 = t1 * fw1, u0 = t0 * fu0, u1 = t1 * fu1;
       const uint32_t wh = pack_bf16x2(w0, w1), uh = pack_bf16x2(u0, u1);
@@ -977,7 +983,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 struct WsLayout {
   size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, o_f32, carry, total;
   int64_t chunks;
-  int segments, seg_chunks;  // chunk ranges per sequence handled by separate launches
+  int segments;        // chunk ranges per sequence handled by separate launches
+  int seg_begin[9];    // range i covers chunks [seg_begin[i], seg_begin[i+1]) of every sequence
 };
 
 WsLayout ws_layout(const AveGdnArgs& a) {
@@ -986,7 +993,7 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   const size_t recs = (size_t)L.chunks * a.Hv;
   auto up = [](size_t x) { return (x + 1023) & ~(size_t)1023; };
   size_t off = 0;
-  L.chunk_start = off; off = up(off + ((size_t)a.n_seqs + 1) * 4);
+  L.chunk_start = off; off = up(off + ((size_t)a.n_seqs + 1 + (size_t)L.chunks) * 4);  // prefix table + chunk -> sequence map
   L.w_hi = off; off = up(off + recs * REC_W);
   L.w_lo = off; off = up(off + recs * REC_W);
   L.p_hi = off; off = up(off + recs * REC_P);
@@ -998,8 +1005,16 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   // Few long chains (fewer scan CTAs than half the SMs): cut the sequences into ranges so that pass 1 of range i+1 runs
   // on the idle SMs while pass 2 of range i walks its chain.  The state crosses ranges through the carry buffer.
   const int max_chunks = (a.T + C - 1) / C;
-  L.segments = ((int64_t)a.n_seqs * a.Hv <= 74 && max_chunks >= 32) ? 4 : 1;
-  L.seg_chunks = (max_chunks + L.segments - 1) / L.segments;
+  L.segments = ((int64_t)a.n_seqs * a.Hv <= 74 && max_chunks >= 32) ? 5 : 1;
+  L.seg_begin[0] = 0;
+  if (L.segments == 1) {
+    L.seg_begin[1] = 1 << 24;  // every chunk (times 64 still fits an int)
+  } else {
+    // a short first range (its pass 1 is the only one nothing overlaps), then four equal ones
+    const int first = (max_chunks + 15) / 16, rest = (max_chunks - first + 3) / 4;
+    L.seg_begin[1] = first;
+    for (int i = 2; i <= 5; ++i) L.seg_begin[i] = first + (i - 1) * rest;
+  }
   L.carry = off;
   if (L.segments > 1) off = up(off + (size_t)a.n_seqs * a.Hv * D * D * 4);
   L.total = off;
@@ -1028,9 +1043,9 @@ extern "C" int ave_trace_read(long long* host, int n) {
 // runs on a high-priority stream so that, when a range's pass 1 completes and both its pass 2 and the next range's
 // pass 1 become runnable on an empty GPU, the few whole-SM pass-2 CTAs are placed first.
 struct SideStream {
-  cudaStream_t prep = nullptr, scan = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
-  cudaEvent_t done[4] = {};
+  cudaStream_t prep = nullptr, scan = nullptr, norm = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr, join_norm = nullptr;
+  cudaEvent_t done[8] = {}, scanned[8] = {};
 };
 static SideStream* side_stream(int dev) {
   static SideStream per_dev[64];
@@ -1040,12 +1055,38 @@ static SideStream* side_stream(int dev) {
     if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithPriority(&s.prep, cudaStreamNonBlocking, lo) != cudaSuccess) { s.prep = nullptr; return nullptr; }
     bool ok = cudaStreamCreateWithPriority(&s.scan, cudaStreamNonBlocking, hi) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithPriority(&s.norm, cudaStreamNonBlocking, lo) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
-    for (int i = 0; i < 4; ++i) ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s.join_norm, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 8; ++i) {
+      ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
+      ok = ok && cudaEventCreateWithFlags(&s.scanned[i], cudaEventDisableTiming) == cudaSuccess;
+    }
     if (!ok) return nullptr;
   }
   return &s;
+}
+
+// Gated RMSNorm over the fp32 output for tokens [t_begin, t_end) of every batch row.
+static int norm_rows(const AveGdnArgs& a, float* o_f32, int t_begin, int t_end, cudaStream_t stream) {
+  if (t_end <= t_begin) return AVE_GDN_OK;
+  for (int b = 0; b < a.B; ++b) {
+    AveGdnNormArgs nb{};
+    nb.struct_size = sizeof(nb);
+    nb.flags = a.flags & AVE_GDN_FLAG_GATE_FIRST;
+    nb.rows = (int64_t)(t_end - t_begin) * a.Hv;
+    nb.d = D; nb.heads = a.Hv; nb.eps = a.norm_eps; nb.weight = a.norm_weight;
+    nb.x = o_f32 + ((int64_t)b * a.T + t_begin) * a.Hv * D;
+    nb.x_stride_t = (int64_t)a.Hv * D; nb.x_stride_h = D;
+    nb.z = reinterpret_cast<const __nv_bfloat16*>(a.z) + b * a.z_stride_b + (int64_t)t_begin * a.z_stride_t;
+    nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
+    nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t;
+    nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
+    const int rc = launch_gated_rmsnorm_f32in(nb, stream);
+    if (rc != AVE_GDN_OK) return rc;
+  }
+  return AVE_GDN_OK;
 }
 
 int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream) {
@@ -1083,7 +1124,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     if ((rc = make_tmap(&maps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.v), 4, dv4, sv, boxv, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
 
-  if (a.cu_seqlens != nullptr) chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start);
+  if (a.cu_seqlens != nullptr) chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start, (int)L.chunks);
   constexpr size_t smem_prep = PREP_SMEM;
   static bool attr_set_dev[64] = {};
   int dev = 0;
@@ -1098,6 +1139,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
   const dim3 prep_grid((unsigned)L.chunks, (unsigned)a.Hv);
   const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)a.Hv;
   SideStream* side = (L.segments > 1 && allow_side_stream) ? side_stream(dev) : nullptr;
+  bool norm_done = a.z == nullptr;
   if (side == nullptr) {
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
@@ -1105,40 +1147,42 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry, 0, big);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
-    // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on the other once pass 1 of range i is
-    // done; both fork from the caller's stream and join back into it through events
+    // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
+    // done, and (dense layouts) the gated norm of range i on a third once pass 2 of range i is done; all fork from the
+    // caller's stream and join back into it through events
+    const bool norm_per_range = a.z != nullptr && a.cu_seqlens == nullptr;
     AVE_CUDA_TRY(cudaEventRecord(side->fork, stream));
     AVE_CUDA_TRY(cudaStreamWaitEvent(side->prep, side->fork, 0));
     AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->fork, 0));
+    if (norm_per_range) AVE_CUDA_TRY(cudaStreamWaitEvent(side->norm, side->fork, 0));
     for (int i = 0; i < L.segments; ++i) {
-      chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * L.seg_chunks), (unsigned)a.Hv), PREP_THREADS, smem_prep, side->prep>>>(
-          a, maps, chunk_start, po, i * L.seg_chunks, L.seg_chunks, 1);
+      const int c0 = L.seg_begin[i], cn = L.seg_begin[i + 1] - L.seg_begin[i];
+      if (cn <= 0) continue;
+      chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * cn), (unsigned)a.Hv), PREP_THREADS, smem_prep, side->prep>>>(
+          a, maps, chunk_start, po, c0, cn, 1);
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry,
-                                                                            i * L.seg_chunks, L.seg_chunks);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry, c0, cn);
       AVE_CUDA_TRY(cudaGetLastError());
+      if (norm_per_range) {
+        AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
+        AVE_CUDA_TRY(cudaStreamWaitEvent(side->norm, side->scanned[i], 0));
+        const int rc = norm_rows(a, o_f32, min(a.T, c0 * C), min(a.T, (c0 + cn) * C), side->norm);
+        if (rc != AVE_GDN_OK) return rc;
+      }
     }
     AVE_CUDA_TRY(cudaEventRecord(side->join, side->scan));
     AVE_CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
-  }
-  if (a.z != nullptr) {  // gated RMSNorm over the fp32 output, one launch per batch row
-    for (int b = 0; b < a.B; ++b) {
-      AveGdnNormArgs nb{};
-      nb.struct_size = sizeof(nb);
-      nb.flags = a.flags & AVE_GDN_FLAG_GATE_FIRST;
-      nb.rows = (int64_t)a.T * a.Hv;
-      nb.d = D; nb.heads = a.Hv; nb.eps = a.norm_eps; nb.weight = a.norm_weight;
-      nb.x = o_f32 + (int64_t)b * a.T * a.Hv * D;
-      nb.x_stride_t = (int64_t)a.Hv * D; nb.x_stride_h = D;
-      nb.z = reinterpret_cast<const __nv_bfloat16*>(a.z) + b * a.z_stride_b;
-      nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
-      nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_stride_b;
-      nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
-      const int rc = launch_gated_rmsnorm_f32in(nb, stream);
-      if (rc != AVE_GDN_OK) return rc;
+    if (norm_per_range) {
+      AVE_CUDA_TRY(cudaEventRecord(side->join_norm, side->norm));
+      AVE_CUDA_TRY(cudaStreamWaitEvent(stream, side->join_norm, 0));
+      norm_done = true;
     }
+  }
+  if (!norm_done) {
+    const int rc = norm_rows(a, o_f32, 0, a.T, stream);
+    if (rc != AVE_GDN_OK) return rc;
   }
   return AVE_GDN_OK;
 }
