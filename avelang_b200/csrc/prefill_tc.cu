@@ -588,6 +588,13 @@ constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO 
                    TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
 
 
+// bf16 hi + lo images of a pair of fp32 values: hi = round-to-bf16, lo = bf16(x - hi); packed math on the pair
+__device__ __forceinline__ void split_pair(float2 x, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16x2(x.x, x.y);
+  const float2 h = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
+  const float2 l = __ffma2_rn(h, make_float2(-1.f, -1.f), x);
+  lo = pack_bf16x2(l.x, l.y);
+}
 __device__ __forceinline__ uint32_t pack_hi(float x0, float x1) { return pack_bf16x2(x0, x1); }
 __device__ __forceinline__ uint32_t pack_lo(float x0, float x1, uint32_t hi_packed) {
   const float h0 = __uint_as_float(hi_packed << 16), h1 = __uint_as_float(hi_packed & 0xffff0000u);
@@ -798,25 +805,23 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     bool alive = true;
     uint32_t sync_phase = 0;
 
-    float Hreg[64];  // H[d][64*grp + i] = M[64*grp + i][d]
+    float2 Hreg[32];  // H[d][64*grp + 2w .. +1] = M[64*grp + 2w .. +1][d]
     const float* state_in = seg_first ? (a.initial_state ? a.initial_state + tile : nullptr) : carry + carry_tile;
     float* state_out = seg_last ? (a.final_state ? a.final_state + tile : nullptr) : carry + carry_tile;
     if (state_in != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) Hreg[i] = state_in[(int64_t)(64 * grp + i) * D + d];
+      for (int w = 0; w < 32; ++w)
+        Hreg[w] = make_float2(state_in[(int64_t)(64 * grp + 2 * w) * D + d], state_in[(int64_t)(64 * grp + 2 * w + 1) * D + d]);
     } else {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) Hreg[i] = 0.f;
+      for (int w = 0; w < 32; ++w) Hreg[w] = make_float2(0.f, 0.f);
     }
     auto publish_h = [&]() {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          hi[w] = pack_hi(Hreg[32 * half + 2 * w], Hreg[32 * half + 2 * w + 1]);
-          lo[w] = pack_lo(Hreg[32 * half + 2 * w], Hreg[32 * half + 2 * w + 1], hi[w]);
-        }
+        for (int w = 0; w < 16; ++w) split_pair(Hreg[16 * half + w], hi[w], lo[w]);
         tc::tmem_st16(lane_addr + TM_HHI + 32 * grp + 16 * half, hi);
         tc::tmem_st16(lane_addr + TM_HLO + 32 * grp + 16 * half, lo);
       }
@@ -840,15 +845,15 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       {
         uint32_t acc[32];
         tc::tmem_ld32(lane_addr + TM_VN + 32 * grp, acc);
-        float v[32];
+        float2 v[16];
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 uq = *reinterpret_cast<const float4*>(u_s + d * U_LD + 32 * grp + 4 * j4);
-          v[4 * j4] = uq.x; v[4 * j4 + 1] = uq.y; v[4 * j4 + 2] = uq.z; v[4 * j4 + 3] = uq.w;
+          v[2 * j4] = make_float2(uq.x, uq.y); v[2 * j4 + 1] = make_float2(uq.z, uq.w);
         }
         tc::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(acc[j]);
+        for (int w = 0; w < 16; ++w) v[w] = __fadd2_rn(v[w], make_float2(__uint_as_float(acc[2 * w]), __uint_as_float(acc[2 * w + 1])));
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(u_empty);
         {  // Vd first: its columns alias nothing, and the state update waits only for it
@@ -856,9 +861,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 #pragma unroll
           for (int w = 0; w < 16; ++w) {
             const float2 ks = *reinterpret_cast<const float2*>(scal + C + 32 * grp + 2 * w);
-            const float e0 = v[2 * w] * ks.x, e1 = v[2 * w + 1] * ks.y;
-            dh[w] = pack_hi(e0, e1);
-            dl[w] = pack_lo(e0, e1, dh[w]);
+            split_pair(__fmul2_rn(v[w], ks), dh[w], dl[w]);
           }
           tc::tmem_st16(lane_addr + TM_VDHI + 16 * grp, dh);
           tc::tmem_st16(lane_addr + TM_VDLO + 16 * grp, dl);
@@ -872,7 +875,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         {
           uint32_t vh[16], vl[16];
 #pragma unroll
-          for (int w = 0; w < 16; ++w) { vh[w] = pack_hi(v[2 * w], v[2 * w + 1]); vl[w] = pack_lo(v[2 * w], v[2 * w + 1], vh[w]); }
+          for (int w = 0; w < 16; ++w) split_pair(v[w], vh[w], vl[w]);
           tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
           tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
           tc::tmem_st_wait();
@@ -893,7 +896,9 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           tc::tmem_ld32(lane_addr + TM_DH + 64 * grp + 32 * half, dh);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) Hreg[32 * half + i] = fmaf(decay, Hreg[32 * half + i], __uint_as_float(dh[i]));
+          for (int w = 0; w < 16; ++w)
+            Hreg[16 * half + w] = __ffma2_rn(make_float2(decay, decay), Hreg[16 * half + w],
+                                             make_float2(__uint_as_float(dh[2 * w]), __uint_as_float(dh[2 * w + 1])));
         }
         publish_h();
       }
@@ -902,7 +907,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
     if (alive && state_out != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) state_out[(int64_t)(64 * grp + i) * D + d] = Hreg[i];
+      for (int w = 0; w < 32; ++w) {
+        state_out[(int64_t)(64 * grp + 2 * w) * D + d] = Hreg[w].x;
+        state_out[(int64_t)(64 * grp + 2 * w + 1) * D + d] = Hreg[w].y;
+      }
     }
   } else {
     tc::reg_set<REGS_OUT, 128>();
@@ -942,10 +950,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
           const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * part + 4 * j4);
-          ov[4 * j4 + 0] = fmaf(qs.x, __uint_as_float(o1[4 * j4 + 0]), __uint_as_float(o2[4 * j4 + 0]));
-          ov[4 * j4 + 1] = fmaf(qs.y, __uint_as_float(o1[4 * j4 + 1]), __uint_as_float(o2[4 * j4 + 1]));
-          ov[4 * j4 + 2] = fmaf(qs.z, __uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 2]));
-          ov[4 * j4 + 3] = fmaf(qs.w, __uint_as_float(o1[4 * j4 + 3]), __uint_as_float(o2[4 * j4 + 3]));
+          const float2 r0 = __ffma2_rn(make_float2(qs.x, qs.y), make_float2(__uint_as_float(o1[4 * j4]), __uint_as_float(o1[4 * j4 + 1])),
+                                       make_float2(__uint_as_float(o2[4 * j4]), __uint_as_float(o2[4 * j4 + 1])));
+          const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o1[4 * j4 + 3])),
+                                       make_float2(__uint_as_float(o2[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 3])));
+          ov[4 * j4 + 0] = r0.x; ov[4 * j4 + 1] = r0.y; ov[4 * j4 + 2] = r1.x; ov[4 * j4 + 3] = r1.y;
         }
         const int n_here = min(32, len - 32 * part);  // tokens of this half that exist
         if (pf != nullptr) {
