@@ -24,7 +24,8 @@ class GdnArgs(ctypes.Structure):
                 + [("workspace_bytes", U64)]
                 + [(n, I32) for n in ("B", "T", "Hk", "Hv", "dk", "dv", "n_seqs", "num_slots", "chunk", "reserved0")]
                 + [(f"{t}_stride_{d}", I64) for t in ("q", "k", "v", "z", "o") for d in ("b", "t", "h")]
-                + [("g_stride_b", I64), ("g_stride_t", I64), ("scale", F32), ("norm_eps", F32)])
+                + [("g_stride_b", I64), ("g_stride_t", I64), ("scale", F32), ("norm_eps", F32),
+                   ("o_peers", P), ("n_peers", I32), ("reserved1", I32)])
 
 
 class NormArgs(ctypes.Structure):
@@ -85,7 +86,7 @@ def load():
         for name, (res, args) in SYMBOLS.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
-        if lib.ave_gdn_abi_version() != 1:
+        if lib.ave_gdn_abi_version() != 2:
             raise ImportError("libave_gdn_b200.so has an unexpected ABI version")
         _LIB = lib
     return _LIB

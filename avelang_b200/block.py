@@ -85,9 +85,9 @@ class GdnBlockShard:
         self.dt_bias = dt_bias[vh.start:vh.stop].float().to(device).contiguous()
         self.norm_weight = None if norm_weight is None else norm_weight.float().to(device).contiguous()
 
-    def forward_local(self, x: torch.Tensor, cu_seqlens=None) -> torch.Tensor:
+    def forward_local(self, x: torch.Tensor, cu_seqlens=None, out=None, out_peers=None) -> torch.Tensor:
         """x: bf16 [B, T, hidden] (replicated on every rank).  Returns this rank's normalised head outputs
-        [B, T, Hv/G, dv]."""
+        [B, T, Hv/G, dv] (written into ``out`` / scattered to ``out_peers`` when given)."""
         from . import gdn, gemm
         B, T, hidden = x.shape
         y2 = gemm.gemm_pipeline_transposed_b(x.reshape(B * T, hidden), self.w)
@@ -104,13 +104,41 @@ class GdnBlockShard:
         g, beta = gdn.gate_beta(a_in, b_in, self.A_log, self.dt_bias)
         g, beta = g.reshape(B, T, self.hv_local), beta.reshape(B, T, self.hv_local)
         o, _ = gdn.chunk_gated_delta_rule(q, k, v, g, beta, use_qk_l2norm_in_kernel=True, cu_seqlens=cu_seqlens,
-                                          z=z, norm_weight=self.norm_weight)
+                                          z=z, norm_weight=self.norm_weight, out=out, out_peers=out_peers)
         return o
 
-    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None) -> torch.Tensor:
-        """Full block output [B, T, Hv, dv] on every rank: local heads, then an all-gather over the head dimension."""
-        o = self.forward_local(x, cu_seqlens)
-        return gather_heads(o, self.shard.world, group)
+    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None, fused_gather=False) -> torch.Tensor:
+        """Full block output [B, T, Hv, dv] on every rank.  Default: local heads, then an NCCL all-gather over the head
+        dimension.  ``fused_gather=True``: the gated-norm kernel stores each normalised row straight into every rank's
+        output buffer (symmetric memory, plain peer stores over NVLink), bracketed by two barriers."""
+        if not fused_gather or self.shard.world == 1:
+            return gather_heads(self.forward_local(x, cu_seqlens), self.shard.world, group)
+        import torch.distributed as dist
+        B, T, _ = x.shape
+        full, peers = self._symmetric_output(B, T, x.device, group)
+        hl = self.hv_local
+        mine = full[:, :, self.shard.rank * hl:(self.shard.rank + 1) * hl]
+        dist.barrier(group)   # every rank is done reading the previous contents of the buffers
+        self.forward_local(x, cu_seqlens, out=mine, out_peers=peers)
+        dist.barrier(group)   # every rank's stores have landed
+        return full
+
+    def _symmetric_output(self, B, T, device, group):
+        """Output buffer [B, T, Hv, dv] in symmetric memory plus the device array of every rank's base address for this
+        rank's head slice; cached per shape."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        key = (B, T, str(device))
+        cache = self.__dict__.setdefault("_symm_cache", {})
+        if key not in cache:
+            grp = group if group is not None else dist.group.WORLD
+            full = symm.empty((B, T, self.Hv, self.dv), dtype=torch.bfloat16, device=device)
+            handle = symm.rendezvous(full, grp)
+            off = self.shard.rank * self.hv_local * self.dv * full.element_size()
+            peers = torch.tensor([int(p) + off for p in handle.buffer_ptrs], dtype=torch.int64, device=device)
+            cache[key] = (full, peers, handle)
+        full, peers, _ = cache[key]
+        return full, peers
 
 
 def gather_heads(o_local: torch.Tensor, world: int, group=None) -> torch.Tensor:

@@ -45,6 +45,8 @@ static int validate_gdn(const AveGdnArgs* a, bool prefill) {
   if (a->initial_state && !aligned16(a->initial_state)) return AVE_GDN_MISALIGNED;
   if (a->final_state && !aligned16(a->final_state)) return AVE_GDN_MISALIGNED;
   if ((reinterpret_cast<uintptr_t>(a->g) & 3u) || (reinterpret_cast<uintptr_t>(a->beta) & 3u)) return AVE_GDN_MISALIGNED;
+  if (a->n_peers < 0 || (a->n_peers > 0 && a->o_peers == nullptr)) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->n_peers > 0 && (!prefill || a->z == nullptr || a->dk != 128)) return AVE_GDN_UNSUPPORTED;
   return AVE_GDN_OK;
 }
 

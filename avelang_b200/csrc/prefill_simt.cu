@@ -338,7 +338,8 @@ size_t prefill_simt_workspace_bytes(const AveGdnArgs& a) {
   return bytes;
 }
 
-int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream);
+int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers = nullptr, int n_peers = 0,
+                               int64_t peer_off = 0);
 
 template <int DK, int DV>
 static int launch_prefill_t(const AveGdnArgs& a, cudaStream_t stream) {

@@ -1032,7 +1032,8 @@ WsLayout ws_layout(const AveGdnArgs& a) {
 
 }  // namespace
 
-int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream);
+int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers = nullptr, int n_peers = 0,
+                               int64_t peer_off = 0);
 
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
 
@@ -1092,7 +1093,7 @@ static int norm_rows(const AveGdnArgs& a, float* o_f32, int t_begin, int t_end, 
     nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
     nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t;
     nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
-    const int rc = launch_gated_rmsnorm_f32in(nb, stream);
+    const int rc = launch_gated_rmsnorm_f32in(nb, stream, a.o_peers, a.n_peers, (int64_t)b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t);
     if (rc != AVE_GDN_OK) return rc;
   }
   return AVE_GDN_OK;

@@ -9,7 +9,8 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const XT* __restrict
                                                             const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                             int64_t rows, int heads, int64_t xs_t, int64_t xs_h,
                                                             int64_t zs_t, int64_t zs_h, int64_t ys_t, int64_t ys_h,
-                                                            float eps, int gate_first) {
+                                                            float eps, int gate_first, const void* const* __restrict__ peers,
+                                                            int n_peers, int64_t peer_off) {
   constexpr int E = D / 32;  // elements per lane
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -49,17 +50,24 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const XT* __restrict
       const float wv = w ? w[lane * E + i] : 1.0f;
       out[i] = xv[i] * rinv * wv * (gate_first ? 1.0f : silu(zv[i]));
     }
-    __nv_bfloat16* yr = y + t * ys_t + h * ys_h + lane * E;
+    const int64_t yoff = t * ys_t + h * ys_h + lane * E;
     if constexpr (E == 4) {
-      *reinterpret_cast<uint2*>(yr) = make_uint2(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]));
+      const uint2 packed = make_uint2(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]));
+      if (n_peers > 0) {  // fused all-gather: the same row goes to every GPU's buffer (plain peer stores)
+        for (int p = 0; p < n_peers; ++p)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(peers[p])) + peer_off + yoff) = packed;
+      } else {
+        *reinterpret_cast<uint2*>(y + yoff) = packed;
+      }
     } else {
-      *reinterpret_cast<uint32_t*>(yr) = pack_bf16x2(out[0], out[1]);
+      *reinterpret_cast<uint32_t*>(y + yoff) = pack_bf16x2(out[0], out[1]);
     }
   }
 }
 
 template <typename XT>
-static int launch_norm_t(const XT* x, const AveGdnNormArgs& a, cudaStream_t stream) {
+static int launch_norm_t(const XT* x, const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers = nullptr, int n_peers = 0,
+                         int64_t peer_off = 0) {
   if (a.rows == 0) return AVE_GDN_OK;
   const int64_t blocks_needed = (a.rows + 7) / 8;
   const unsigned grid = (unsigned)(blocks_needed < 148 * 64 ? blocks_needed : 148 * 64);
@@ -68,10 +76,10 @@ static int launch_norm_t(const XT* x, const AveGdnNormArgs& a, cudaStream_t stre
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(a.y);
   if (a.d == 128) {
     gated_rmsnorm_kernel<128, XT><<<grid, 256, 0, stream>>>(x, z, a.weight, y, a.rows, a.heads, a.x_stride_t, a.x_stride_h,
-                                                            a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first);
+                                                            a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first, peers, n_peers, peer_off);
   } else if (a.d == 64) {
     gated_rmsnorm_kernel<64, XT><<<grid, 256, 0, stream>>>(x, z, a.weight, y, a.rows, a.heads, a.x_stride_t, a.x_stride_h,
-                                                           a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first);
+                                                           a.z_stride_t, a.z_stride_h, a.y_stride_t, a.y_stride_h, a.eps, gate_first, nullptr, 0, 0);
   } else {
     return AVE_GDN_UNSUPPORTED;
   }
@@ -84,8 +92,8 @@ int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream) {
 }
 
 // fp32 input variant used by the prefill path when the un-normalised output is staged in scratch
-int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream) {
-  return launch_norm_t(reinterpret_cast<const float*>(a.x), a, stream);
+int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers, int n_peers, int64_t peer_off) {
+  return launch_norm_t(reinterpret_cast<const float*>(a.x), a, stream, peers, n_peers, peer_off);
 }
 
 }  // namespace ave

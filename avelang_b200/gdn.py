@@ -168,12 +168,17 @@ def _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, device, want_
 
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                            use_qk_l2norm_in_kernel=False, cu_seqlens=None, *, z=None, norm_weight=None,
-                           norm_eps=1e-6, state_indices=None, inplace_state=True, chunk_size=64, out=None):
+                           norm_eps=1e-6, state_indices=None, inplace_state=True, chunk_size=64, out=None, out_peers=None):
     """Chunked (chunk 64) gated delta rule over whole sequences.  Returns ``(o, final_state or None)``.
 
     With ``z`` the gated RMSNorm ``rmsnorm(o) * silu(z)`` (weight ``norm_weight``, eps ``norm_eps``) is fused and
     ``o`` is the normalised output.  With ``state_indices`` the initial states are read from, and the final
-    states written to, slots of the ``initial_state`` pool (in place unless ``inplace_state=False``)."""
+    states written to, slots of the ``initial_state`` pool (in place unless ``inplace_state=False``).
+
+    ``out_peers`` (needs ``z``): int64 device tensor of base addresses of buffers laid out exactly like ``out``, one per
+    GPU of the node (peer-mapped, this GPU's included).  The normalised rows are then stored into all of them by the
+    norm kernel itself (a fused all-gather over NVLink) instead of into ``out``; the caller must put a barrier between
+    this call and any reader of those buffers."""
     B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, z, cu_seqlens)
     _req(chunk_size == 64, f"chunk_size must be 64, got {chunk_size}.")
     o = _prep_out(out, v, z)
@@ -183,6 +188,11 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
     a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
                    state_indices, num_slots, n_seqs, flags)
+    if out_peers is not None:
+        _req(z is not None, "out_peers needs z (the stores are fused into the gated norm)")
+        _req(out_peers.dtype == torch.int64 and out_peers.dim() == 1 and out_peers.device == q.device and out_peers.is_contiguous(),
+             f"out_peers must be a contiguous 1-D int64 tensor on {q.device}")
+        a.o_peers, a.n_peers = out_peers.data_ptr(), out_peers.numel()
     lib = _lib.load()
     with torch.cuda.device(q.device):
         nbytes = lib.ave_gdn_prefill_workspace_bytes(ctypes.byref(a))

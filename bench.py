@@ -300,7 +300,8 @@ def bench_block(args, rank, world):
     x = torch.randn(B, T, hidden, generator=gen).bfloat16().cuda()
     blk = GdnBlockShard(w_in, conv_w, A_log, dt_bias, torch.ones(D), Hk=HK, Hv=HV, dk=D, dv=D, rank=rank, world=world)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
-    step = lambda: blk.forward(x)
+    fused = os.environ.get("AVE_GDN_FUSED_GATHER", "1") != "0"  # peer-store all-gather fused into the norm kernel
+    step = lambda: blk.forward(x, fused_gather=fused)
     with ClockSampler(torch.cuda.current_device()) as clocks:
         total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
     ms = total_ms / args.steps
@@ -312,7 +313,7 @@ def bench_block(args, rank, world):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "GDN block B=4 T=32768 hidden 2048: in-proj, conv1d k=4 + SiLU, L2 norm, gate/beta, "
                                    "chunked delta rule, gated RMSNorm, head all-gather",
-                       "parallelism": f"heads sharded x{world}, one NCCL all-gather", "l2": "256 MiB flush write before every timed step"},
+                       "parallelism": f"heads sharded x{world}, " + ("all-gather fused into the norm kernel (peer stores)" if fused else "one NCCL all-gather"), "l2": "256 MiB flush write before every timed step"},
             "gpu_launches": 6 * args.steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] * world, "unit": "TFLOP/s",
                          "frac": achieved / (peaks["bf16_tflops_sustained"] * world), "traffic": None,

@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define AVE_GDN_ABI_VERSION 1
+#define AVE_GDN_ABI_VERSION 2
 
 typedef enum AveGdnStatus {
   AVE_GDN_OK = 0,
@@ -88,6 +88,13 @@ typedef struct AveGdnArgs {
   int64_t g_stride_b, g_stride_t; /* g and beta share strides; head stride is 1 */
   float scale;
   float norm_eps;
+  /* Optional fused all-gather of the output (prefill with z only): a device array of n_peers base pointers of buffers
+   * laid out exactly like `o` (one per GPU of the node, peer-mapped, this GPU's own buffer included).  The gated-norm
+   * stage then stores every output row into all of them with plain peer stores instead of into `o`; `o` still defines
+   * the layout.  The caller orders the stores against the peers' readers (a barrier after the call). */
+  const void* const* o_peers;
+  int32_t n_peers;
+  int32_t reserved1;
 } AveGdnArgs;
 
 /* Chunked prefill (chunk 64, WY/UT form), dense [B,T] or packed varlen via cu_seqlens. */

@@ -1,0 +1,61 @@
+"""GPU tests of the fused all-gather: the gated-norm stage stores every output row into all given buffers."""
+import os
+import socket
+
+import pytest
+import torch
+
+from avelang_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def test_peer_scatter_single_gpu(built_lib):
+    """Two buffers on one GPU stand in for two ranks: both must receive the rows, at the head slice's offsets."""
+    from avelang_b200 import gdn
+    inp = synth.make_inputs(2, 200, 2, 4, 128, 128, seed=3, with_z=True, gate_scale=0.1).to("cuda")
+    ref, _ = gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, z=inp.z)
+    # the local output is heads [4, 8) of a 12-head buffer
+    bufs = [torch.zeros(2, 200, 12, 128, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    off = 4 * 128 * 2
+    peers = torch.tensor([b.data_ptr() + off for b in bufs], dtype=torch.int64, device="cuda")
+    gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, z=inp.z, out=bufs[0][:, :, 4:8], out_peers=peers)
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert torch.equal(b[:, :, 4:8], ref)
+        assert torch.count_nonzero(b[:, :, :4]) == 0 and torch.count_nonzero(b[:, :, 8:]) == 0
+    with pytest.raises(ValueError):
+        gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, out_peers=peers)  # needs z
+
+
+def _rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+    from avelang_b200.block import GdnBlockShard
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        hidden, Hk, Hv, d, B, T = 256, 2, 4, 128, 2, 200
+        g = torch.Generator().manual_seed(0)
+        w_in = (0.02 * torch.randn(2 * Hk * d + 2 * Hv * d + 2 * Hv, hidden, generator=g)).bfloat16()
+        conv_w = (torch.randn(2 * Hk * d + Hv * d, 4, generator=g) / 2).bfloat16()
+        A_log, dt_bias = torch.rand(Hv, generator=g) * 2.77, 0.1 * torch.randn(Hv, generator=g)
+        x = torch.randn(B, T, hidden, generator=g).bfloat16().cuda()
+        blk = GdnBlockShard(w_in, conv_w, A_log, dt_bias, torch.ones(d), Hk=Hk, Hv=Hv, dk=d, dv=d, rank=rank, world=world)
+        y_nccl = blk.forward(x)
+        y_fused = blk.forward(x, fused_gather=True).clone()
+        ret[rank] = bool(torch.equal(y_nccl, y_fused))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_gather_matches_nccl_two_ranks(built_lib):
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(2, port, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: True, 1: True}
