@@ -397,7 +397,9 @@ def main():
                           "config": {"workload": "256 seqs x 32 value heads, T=1, 512-slot fp32 pool [128x128], in place"},
                           "roofline": {"bound": "hbm", "achieved": all_bytes / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": all_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                                       "frac_of_nominal_8TBps": all_bytes / (us * 1e-6) / 8e12, "traffic": None,
+                                       "frac_of_nominal_8TBps": all_bytes / (us * 1e-6) / 8e12,
+                                       "traffic": 1_020_755_968,  # dram read+write per launch, ncu capture at full size
+                                       "traffic_source": "profiles/decode_gdn_decode_kernel_config2.md",
                                        "peak_source": peaks["source"]}}
     if world > 1:
         barrier(world)
