@@ -54,30 +54,45 @@ __global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, i
       for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
     }
   }
-  for (int t = t_begin; t < t_end; ++t) {
-    if (a.cu_seqlens != nullptr && t >= seq_end) {  // crossed into the next sequence: forget history
-      while (t >= seq_end && seq + 1 < a.n_seqs) { ++seq; seq_start = seq_end; seq_end = a.cu_seqlens[seq + 1]; }
+  // tokens are fetched eight at a time so that eight 16-byte loads are in flight per thread
+  for (int tb = t_begin; tb < t_end; tb += 8) {
+    uint4 raw[8];
 #pragma unroll
-      for (int j = 0; j < WIDTH - 1; ++j)
+    for (int j = 0; j < 8; ++j)
+      raw[j] = (tb + j < t_end) ? *reinterpret_cast<const uint4*>(xg + (int64_t)(tb + j) * a.x_stride_t) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
+    for (int j = 0; j < 8; ++j) {
+      const int t = tb + j;
+      if (t >= t_end) break;
+      if (a.cu_seqlens != nullptr && t >= seq_end) {  // crossed into the next sequence: forget history
+        while (t >= seq_end && seq + 1 < a.n_seqs) { ++seq; seq_start = seq_end; seq_end = a.cu_seqlens[seq + 1]; }
+#pragma unroll
+        for (int jj = 0; jj < WIDTH - 1; ++jj)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) hist[jj][c] = 0.f;
+      }
+      const uint4 rw = raw[j];
+      float* cur = hist[WIDTH - 1];
+      cur[0] = __uint_as_float(rw.x << 16); cur[1] = __uint_as_float(rw.x & 0xffff0000u);
+      cur[2] = __uint_as_float(rw.y << 16); cur[3] = __uint_as_float(rw.y & 0xffff0000u);
+      cur[4] = __uint_as_float(rw.z << 16); cur[5] = __uint_as_float(rw.z & 0xffff0000u);
+      cur[6] = __uint_as_float(rw.w << 16); cur[7] = __uint_as_float(rw.w & 0xffff0000u);
+      float out[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float acc = bias[c];
+#pragma unroll
+        for (int jj = 0; jj < WIDTH; ++jj) acc = fmaf(w[c][jj], hist[jj][c], acc);
+        out[c] = silu(acc);
+      }
+      const uint4 packed = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]),
+                                      pack_bf16x2(out[4], out[5]), pack_bf16x2(out[6], out[7]));
+      *reinterpret_cast<uint4*>(yg + (int64_t)t * a.y_stride_t) = packed;
+#pragma unroll
+      for (int jj = 0; jj < WIDTH - 1; ++jj)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) hist[jj][c] = hist[jj + 1][c];
     }
-    load8(t, hist[WIDTH - 1]);
-    float out[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      float acc = bias[c];
-#pragma unroll
-      for (int j = 0; j < WIDTH; ++j) acc = fmaf(w[c][j], hist[j][c], acc);
-      out[c] = silu(acc);
-    }
-    uint4 packed = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]),
-                              pack_bf16x2(out[4], out[5]), pack_bf16x2(out[6], out[7]));
-    *reinterpret_cast<uint4*>(yg + (int64_t)t * a.y_stride_t) = packed;
-#pragma unroll
-    for (int j = 0; j < WIDTH - 1; ++j)
-#pragma unroll
-      for (int c = 0; c < 8; ++c) hist[j][c] = hist[j + 1][c];
   }
 }
 
