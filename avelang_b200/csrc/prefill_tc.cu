@@ -162,22 +162,26 @@ __device__ __forceinline__ void block_store(float* __restrict__ dst, const float
 constexpr int PREP_THREADS = 256;
 constexpr int U_LD = 68;                              // row stride (floats) of U^T: 16-byte rows, conflict-free float4 reads
 constexpr int U_REC_BYTES = D * U_LD * 4;             // 34816
-constexpr int PP_KQ = 0, PP_V = 32768, PP_T = 49152,  // PP_T: Tw_hi | Tw_lo | Tu_hi | Tu_lo, bf16 [64][64] K-major tiles
-              PP_A = PP_T + 4 * 8192,                 // A, later T: 10 lower-triangular 16x16 fp32 blocks
-              PP_DI = PP_A + 10 * BLK_FLOATS * 4,     // inverses of the 4 diagonal blocks
-              PP_SC = PP_DI + 4 * BLK_FLOATS * 4, PP_BARS = PP_SC + 4 * C * 4;
-// E (6 blocks), E^2 (3) and E^3 (1) are dead before the operand tiles are written, so they borrow the tile region
-constexpr int PP_E = PP_T, PP_E2 = PP_E + 6 * BLK_FLOATS * 4, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
-static_assert(PP_E3 + BLK_FLOATS * 4 <= PP_T + 4 * 8192, "block scratch must fit inside the tile region");
+// Regions are reused as their contents die, which keeps a CTA under 70 KB so that three fit on an SM:
+//   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   the Q halves later hold Tw hi / Tw lo; after the W MMA the region is store staging
+//   PP_R1  E, E^2, E^3 block scratch       later Tu hi | Tu lo, then store staging
+//   PP_R2  A -> T blocks and D^-1 blocks   later the V tile (loaded only once the blocks are dead)
+constexpr int PP_KQ = 0, PP_TWH = PP_KQ + 8192, PP_TWL = PP_KQ + 24576,
+              PP_R1 = 32768, PP_TUH = PP_R1, PP_TUL = PP_R1 + 8192,
+              PP_R2 = 49152, PP_A = PP_R2, PP_DI = PP_A + 10 * BLK_FLOATS * 4, PP_V = PP_R2,
+              PP_SC = PP_R2 + 18432, PP_BARS = PP_SC + 4 * C * 4;
+constexpr int PP_E = PP_R1, PP_E2 = PP_E + 6 * BLK_FLOATS * 4, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
+static_assert(PP_E3 + BLK_FLOATS * 4 <= PP_R1 + 16384, "block scratch must fit inside its region");
+static_assert(PP_DI + 4 * BLK_FLOATS * 4 <= PP_R2 + 18432, "T and D^-1 blocks must fit inside their region");
 constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
-constexpr uint32_t PT_GRAM = 0, PT_W = 64, PT_U = 128;  // TMEM columns (256 allocated)
+constexpr uint32_t PT_GRAM = 0, PT_W = 0, PT_U = 64;    // TMEM columns (128 allocated; W^T reuses the Gram columns)
 
 // Pass 1 per (chunk, value head):
 //   tensor cores: [K; Q] K^T                                   -> A (strict lower, gated) and P (lower, gated)
 //   CUDA cores  : T = (I + A)^-1 by forward substitution (4 threads per column, rows interleaved mod 4)
 //   tensor cores: W^T = K^T (T diag(beta e^b))^T,  U^T = V^T (T diag(beta))^T   (M = 128 = d_k / d_v, N = 64 tokens)
 // W^T leaves as bf16 hi + lo [128][64] (the scan reads it as an MN-major B operand), U^T as fp32 [128][68].
-__global__ void __launch_bounds__(PREP_THREADS, 2)
+__global__ void __launch_bounds__(PREP_THREADS, 3)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out,
                   int seg_c0, int seg_n, int compact_grid) {
   extern __shared__ uint8_t smem_raw[];
@@ -194,8 +198,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_BARS);
   uint64_t* tma_bar = bars;
   uint64_t* mma_bar = bars + 1;
-  uint64_t* mma2_bar = bars + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint64_t* mma2_bar = bars + 2;   // W^T accumulated
+  uint64_t* mma3_bar = bars + 3;   // U^T accumulated
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int h = blockIdx.y, tid = threadIdx.x;
@@ -220,17 +225,16 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::mbar_init(tma_bar, 1);
     tc::mbar_init(mma_bar, 1);
     tc::mbar_init(mma2_bar, 1);
+    tc::mbar_init(mma3_bar, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
-    tc::mbar_expect_tx(tma_bar, 32768 + 16384);
+    tc::mbar_expect_tx(tma_bar, 32768);
     tc::tma_load_4d(smem + PP_KQ, &maps.k, tma_bar, 0, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 8192, &maps.q, tma_bar, 0, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 16384, &maps.k, tma_bar, 64, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 24576, &maps.q, tma_bar, 64, hk, cr.t0, cr.b);
-    tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
-    tc::tma_load_4d(smem + PP_V + 8192, &maps.v, tma_bar, 64, h, cr.t0, cr.b);
   }
-  if (warp == 2) tc::tmem_alloc(tmem_slot, 256);
+  if (warp == 2) tc::tmem_alloc(tmem_slot, 128);
   if (tid < C) {
     const bool valid = tid < cr.len;
     const int64_t off = cr.b * a.g_stride_b + (int64_t)(cr.t0 + tid) * a.g_stride_t + h;
@@ -448,49 +452,64 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       const uint32_t off = (uint32_t)(i * 128 + ((((j >> 3) ^ (i & 7))) << 4) + (j & 7) * 2);
       const float w0 = t0 * fw0, w1 = t1 * fw1, u0 = t0 * fu0, u1 = t1 * fu1;
       const uint32_t wh = pack_bf16x2(w0, w1), uh = pack_bf16x2(u0, u1);
-      *reinterpret_cast<uint32_t*>(smem + PP_T + off) = wh;
-      *reinterpret_cast<uint32_t*>(smem + PP_T + 8192 + off) =
+      *reinterpret_cast<uint32_t*>(smem + PP_TWH + off) = wh;
+      *reinterpret_cast<uint32_t*>(smem + PP_TWL + off) =
           pack_bf16x2(w0 - __uint_as_float(wh << 16), w1 - __uint_as_float(wh & 0xffff0000u));
-      *reinterpret_cast<uint32_t*>(smem + PP_T + 16384 + off) = uh;
-      *reinterpret_cast<uint32_t*>(smem + PP_T + 24576 + off) =
+      *reinterpret_cast<uint32_t*>(smem + PP_TUH + off) = uh;
+      *reinterpret_cast<uint32_t*>(smem + PP_TUL + off) =
           pack_bf16x2(u0 - __uint_as_float(uh << 16), u1 - __uint_as_float(uh & 0xffff0000u));
     }
   }
   tc::fence_proxy_async_smem();
   __syncthreads();
+  // The T and D^-1 blocks are dead now: the V tile takes their place while W^T is being formed.
+  if (tid == 0 && ok) {
+    tc::mbar_expect_tx(tma_bar, 16384);
+    tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
+    tc::tma_load_4d(smem + PP_V + 8192, &maps.v, tma_bar, 64, h, cr.t0, cr.b);
+  }
+  constexpr uint32_t idesc_wu = tc::idesc_f16(128, 64, 1, 1, true, false);  // A MN-major (token rows), B K-major
   if (warp == 0) {
     const bool leader = tc::elect_one();
     if (ok && leader) {
-      constexpr uint32_t idesc = tc::idesc_f16(128, 64, 1, 1, true, false);  // A MN-major (token rows), B K-major
-      const uint32_t kbase = tc::smem_u32(smem + PP_KQ), vbase = tc::smem_u32(smem + PP_V), tbase = tc::smem_u32(smem + PP_T);
+      const uint32_t kbase = tc::smem_u32(smem + PP_KQ);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
+        const uint32_t tw = tc::smem_u32(smem + (t ? PP_TWL : PP_TWH));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          // K halves sit 16384 bytes apart (Q halves are interleaved), V halves 8192 bytes apart
-          tc::mma_ss(tm + PT_W, tc::smem_desc_sw128(kbase + k * 2048, 16384, 1024), tc::smem_desc_sw128(tbase + t * 8192 + k * 32, 16, 1024),
-                     idesc, (t | k) != 0 ? 1u : 0u);
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          tc::mma_ss(tm + PT_U, tc::smem_desc_sw128(vbase + k * 2048, 8192, 1024),
-                     tc::smem_desc_sw128(tbase + 16384 + t * 8192 + k * 32, 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < 4; ++k)  // K halves sit 16384 bytes apart (the Q halves' slots lie between them)
+          tc::mma_ss(tm + PT_W, tc::smem_desc_sw128(kbase + k * 2048, 16384, 1024), tc::smem_desc_sw128(tw + k * 32, 16, 1024), idesc_wu,
+                     (t | k) != 0 ? 1u : 0u);
       }
       tc::mma_commit(mma2_bar);
     }
     __syncwarp();
+  } else if (warp == 4) {
+    const bool v_ok = ok && tc::mbar_wait(tma_bar, 1, abort_flag);
+    tc::tc_fence_after_sync();
+    const bool leader = tc::elect_one();
+    if (v_ok && leader) {
+      const uint32_t vbase = tc::smem_u32(smem + PP_V);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t tu = tc::smem_u32(smem + (t ? PP_TUL : PP_TUH));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // V halves are adjacent, 8192 bytes apart
+          tc::mma_ss(tm + PT_U, tc::smem_desc_sw128(vbase + k * 2048, 8192, 1024), tc::smem_desc_sw128(tu + k * 32, 16, 1024), idesc_wu,
+                     (t | k) != 0 ? 1u : 0u);
+      }
+      tc::mma_commit(mma3_bar);
+    }
+    __syncwarp();
   }
   PTRACE(8);
+  // warps 0..3 turn W^T into bf16 hi + lo as soon as it is complete; warps 4..7 wait for U^T (issued after W^T)
   ok = ok && tc::mbar_wait(mma2_bar, 0, abort_flag);
+  if (warp >= 4) ok = ok && tc::mbar_wait(mma3_bar, 0, abort_flag);  // a different thread issued U^T: wait for both
   PTRACE(9);
   tc::tc_fence_after_sync();
   {
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // d_k index (warps 0..3) or d_v index (warps 4..7)
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
     // Each lane owns one output row.  A direct store would scatter 32 rows per instruction, so rows are transposed
     // through a per-warp staging area (the K/Q/V tiles are dead by now) with an XOR swizzle on 16-byte pieces and
@@ -530,7 +549,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       }
       PTRACE(12);
     } else {
-      uint4* st = reinterpret_cast<uint4*>(smem + PP_KQ + 16384 + (warp - 4) * 8192);  // 32 rows x 256 B
+      // K_h1 / Tw lo are dead once W^T is complete, the Tu tiles once U^T is complete (and U^T is issued after W^T)
+      uint4* st = reinterpret_cast<uint4*>(smem + (warp < 6 ? PP_KQ + 16384 + (warp - 4) * 8192 : PP_R1 + (warp - 6) * 8192));  // 32 rows x 256 B
       float* gu = out.u + rec * (D * U_LD) + (quarter * 32) * U_LD;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -555,7 +575,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   __syncthreads();
   if (warp == 2) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tm, 256);
+    tc::tmem_dealloc(tm, 128);
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
   PTRACE(10);
