@@ -1,18 +1,21 @@
 // Chunked gated-delta-rule prefill on the tensor cores (d_k = d_v = 128, chunk 64).
 //
-// Pass 1, chunk_prep (one CTA per (chunk, value head), fully parallel): in-chunk cumulative gate b,
-//   A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j), forward substitution for W = (I+A)^-1 diag(beta e^b) K and
-//   U = (I+A)^-1 diag(beta) V, P = lower_incl(e^{b_i-b_j} q_i.k_j).  W and P leave as bf16 hi+lo pairs (the
-//   tensor cores then see 16 significant bits), U as fp32, plus per-token scale vectors.
+// Pass 1, chunk_prep (one CTA per (chunk, value head), fully parallel, three CTAs per SM): in-chunk cumulative gate b,
+//   [K; Q] K^T on tcgen05 -> A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j) and P = scale * lower_incl(e^{b_i-b_j} q_i.k_j);
+//   T = (I+A)^-1 by 16x16 blocks (warp-level tf32 MMAs); W^T = K^T (T diag(beta e^b))^T and U^T = V^T (T diag(beta))^T on
+//   tcgen05.  W^T and P leave as bf16 hi+lo pairs (the tensor cores then see 16 significant bits), U^T as fp32, plus
+//   per-token scale vectors.
 // Pass 2, chunk_scan (one CTA per (sequence, value head)): the recurrence over chunks with the state kept
 //   on chip, transposed (H = M^T, rows = d_v = TMEM lanes) so that every MMA has M = 128:
-//     Vn^T = U^T - H W^T                 (A = H hi/lo from TMEM, B = W hi/lo, K-major)
-//     O^T  = diag-scaled H Q^T + Vn^T P^T (A = H or Vn hi/lo from TMEM, B = Q or P hi/lo, K-major)
-//     H   <- e^{b_C} H + Vd^T K          (A = Vd hi/lo from TMEM, B = K, MN-major), Vd_j = e^{b_C-b_j} Vn_j
-//   fp32 master copy of H lives in the epilogue threads' registers; its bf16 hi/lo image is rewritten to TMEM
-//   every chunk.  Warp roles: 0 = TMA loader, 1 = MMA issuer, 2..9 = two epilogue groups (each covers all
-//   128 TMEM lanes and half of the columns).  All waits are bounded; on give-up the CTA drains and sets a
-//   status bit.
+//     Vn^T = U^T - H W^T                  (A = H hi/lo from TMEM, B = W^T hi/lo read MN-major)
+//     O^T  = qs-scaled H Q^T + Vn^T P^T   (A = H or Vn hi/lo from TMEM, B = Q or P hi/lo, K-major)
+//     H   <- e^{b_C} H + Vd^T K           (A = Vd hi/lo from TMEM, B = K, MN-major), Vd_j = e^{b_C-b_j} Vn_j
+//   The fp32 master copy of H lives in the chain-epilogue threads' registers; its bf16 hi/lo image is rewritten to
+//   TMEM every chunk.  Four warpgroups with redistributed register budgets: control (warp 0 = TMA loader, warp 1 = MMA
+//   issuer), two chain-epilogue groups (each covers all 128 TMEM lanes and half of the columns), one output group.
+//   With a gate tensor z the un-normalised output goes to fp32 scratch and a gated-RMSNorm launch finishes it
+//   (optionally storing each row into every GPU's buffer: the fused all-gather).
+// All waits are bounded; on give-up the CTA drains, frees its tensor memory and sets a status bit.
 #include "common.cuh"
 #include "tc.cuh"
 
@@ -73,11 +76,6 @@ __global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, in
     for (int i = 0; i < cnt && run + i < max_chunks; ++i) chunk_seq[run + i] = n;
     run += cnt;
   }
-}
-
-__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
-  hi = __float2bfloat16(x);
-  lo = __float2bfloat16(x - __bfloat162float(hi));
 }
 
 #ifdef AVE_TRACE
@@ -614,11 +612,6 @@ __device__ __forceinline__ void split_pair(float2 x, uint32_t& hi, uint32_t& lo)
   const float2 h = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
   const float2 l = __ffma2_rn(h, make_float2(-1.f, -1.f), x);
   lo = pack_bf16x2(l.x, l.y);
-}
-__device__ __forceinline__ uint32_t pack_hi(float x0, float x1) { return pack_bf16x2(x0, x1); }
-__device__ __forceinline__ uint32_t pack_lo(float x0, float x1, uint32_t hi_packed) {
-  const float h0 = __uint_as_float(hi_packed << 16), h1 = __uint_as_float(hi_packed & 0xffff0000u);
-  return pack_bf16x2(x0 - h0, x1 - h1);
 }
 // Barrier among a group of warps built on an mbarrier so that, unlike bar.sync, the wait is bounded.
 __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
