@@ -46,6 +46,12 @@ class ConvArgs(ctypes.Structure):
                 ("x_stride_b", I64), ("x_stride_t", I64), ("y_stride_b", I64), ("y_stride_t", I64)]
 
 
+class ConvUpdateArgs(ctypes.Structure):
+    _fields_ = [("struct_size", U32), ("flags", U32), ("x", P), ("w", P), ("bias", P), ("y", P), ("conv_state", P),
+                ("state_indices", P), ("n_seqs", I32), ("C", I32), ("width", I32), ("num_slots", I32),
+                ("x_stride", I64), ("y_stride", I64)]
+
+
 class GateArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("A_log", P), ("dt_bias", P),
                 ("g", P), ("beta", P), ("rows", I64), ("Hv", I32), ("reserved0", I32),
@@ -61,6 +67,7 @@ SYMBOLS = {
     "ave_gdn_gated_rmsnorm": (ctypes.c_int, [ctypes.POINTER(NormArgs), P]),
     "ave_gemm_bf16_nt": (ctypes.c_int, [ctypes.POINTER(GemmArgs), P]),
     "ave_gdn_conv1d_silu": (ctypes.c_int, [ctypes.POINTER(ConvArgs), P]),
+    "ave_gdn_conv1d_update": (ctypes.c_int, [ctypes.POINTER(ConvUpdateArgs), P]),
     "ave_gdn_gate_beta": (ctypes.c_int, [ctypes.POINTER(GateArgs), P]),
     "ave_gdn_abi_version": (ctypes.c_int, []),
     "ave_gdn_status_string": (ctypes.c_char_p, [ctypes.c_int]),

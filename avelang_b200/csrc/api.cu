@@ -13,6 +13,7 @@ size_t prefill_tc_workspace_bytes(const AveGdnArgs& a);
 int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream);
 int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
+int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
 
 static size_t prefill_ws_bytes(const AveGdnArgs& a) {
@@ -118,6 +119,16 @@ int ave_gdn_conv1d_silu(const AveConvArgs* a, void* stream) {
   if (!aligned16(a->x) || !aligned16(a->y) || (a->x_stride_t % 8) || (a->y_stride_t % 8) || (a->x_stride_b % 8) || (a->y_stride_b % 8))
     return AVE_GDN_MISALIGNED;
   return launch_conv1d_silu(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ave_gdn_conv1d_update(const AveConvUpdateArgs* a, void* stream) {
+  if (a == nullptr || a->struct_size != sizeof(AveConvUpdateArgs) || a->n_seqs < 0 || a->C < 0 || a->num_slots < 0) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->width < 2 || a->width > 4 || a->C % 8) return AVE_GDN_UNSUPPORTED;
+  if (a->n_seqs == 0 || a->C == 0) return AVE_GDN_OK;
+  if (!a->x || !a->w || !a->y || !a->conv_state) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->state_indices == nullptr && a->num_slots < a->n_seqs) return AVE_GDN_INVALID_ARGUMENT;
+  if (!aligned16(a->x) || !aligned16(a->y) || !aligned16(a->conv_state) || (a->x_stride % 8) || (a->y_stride % 8)) return AVE_GDN_MISALIGNED;
+  return launch_conv1d_update(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ave_gdn_gate_beta(const AveGateArgs* a, void* stream) {

@@ -112,6 +112,57 @@ int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream) {
   return AVE_GDN_OK;
 }
 
+// Decode-time convolution: one thread per (sequence, 8 channels); history rows are channel-contiguous, so every access
+// is a coalesced 16-byte piece.
+template <int WIDTH>
+__global__ void __launch_bounds__(128) conv1d_update_kernel(const AveConvUpdateArgs a) {
+  const int cg = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.y;
+  if (cg * 8 >= a.C) return;
+  int slot = a.state_indices ? a.state_indices[n] : n;
+  if (slot < 0 || slot >= a.num_slots) return;
+  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(a.conv_state) + (int64_t)slot * (WIDTH - 1) * a.C + cg * 8;
+  auto unpack8 = [](uint4 raw, float (&f)[8]) {
+    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+    f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xffff0000u);
+    f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xffff0000u);
+  };
+  uint4 raw[WIDTH];
+#pragma unroll
+  for (int j = 0; j < WIDTH - 1; ++j) raw[j] = *reinterpret_cast<const uint4*>(st + (int64_t)j * a.C);
+  raw[WIDTH - 1] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.x) + n * a.x_stride + cg * 8);
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = a.bias ? bf2f(reinterpret_cast<const __nv_bfloat16*>(a.bias)[cg * 8 + c]) : 0.f;
+  const __nv_bfloat16* wg = reinterpret_cast<const __nv_bfloat16*>(a.w) + (int64_t)cg * 8 * WIDTH;
+#pragma unroll
+  for (int j = 0; j < WIDTH; ++j) {
+    float xv[8];
+    unpack8(raw[j], xv);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = fmaf(bf2f(wg[c * WIDTH + j]), xv[c], acc[c]);
+  }
+  uint4 packed = make_uint4(pack_bf16x2(silu(acc[0]), silu(acc[1])), pack_bf16x2(silu(acc[2]), silu(acc[3])),
+                            pack_bf16x2(silu(acc[4]), silu(acc[5])), pack_bf16x2(silu(acc[6]), silu(acc[7])));
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y) + n * a.y_stride + cg * 8) = packed;
+#pragma unroll
+  for (int j = 0; j < WIDTH - 1; ++j) *reinterpret_cast<uint4*>(st + (int64_t)j * a.C) = raw[j + 1];  // shift in the new token
+}
+
+int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream) {
+  if (a.n_seqs == 0 || a.C == 0) return AVE_GDN_OK;
+  dim3 grid((a.C / 8 + 127) / 128, a.n_seqs);
+  switch (a.width) {
+    case 2: conv1d_update_kernel<2><<<grid, 128, 0, stream>>>(a); break;
+    case 3: conv1d_update_kernel<3><<<grid, 128, 0, stream>>>(a); break;
+    case 4: conv1d_update_kernel<4><<<grid, 128, 0, stream>>>(a); break;
+    default: return AVE_GDN_UNSUPPORTED;
+  }
+  AVE_CUDA_TRY(cudaGetLastError());
+  return AVE_GDN_OK;
+}
+
 __global__ void __launch_bounds__(256) gate_beta_kernel(const AveGateArgs a) {
   const int64_t total = a.rows * a.Hv;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {

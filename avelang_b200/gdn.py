@@ -23,7 +23,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "causal_conv1d_silu", "gate_beta",
+__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "causal_conv1d_silu",
+           "causal_conv1d_update", "gate_beta",
            "read_status"]
 
 _status_words: dict[int, torch.Tensor] = {}
@@ -295,6 +296,42 @@ def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, *, out=None):
     with torch.cuda.device(x.device):
         rc = _lib.load().ave_gdn_conv1d_silu(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "causal_conv1d_silu")
+    return out
+
+
+def causal_conv1d_update(x, conv_state, weight, bias=None, state_indices=None, *, out=None):
+    """Decode-time step of ``causal_conv1d_silu``: ``x`` bf16 ``[N, C]`` (one new token per sequence), ``conv_state`` bf16
+    ``[slots, W-1, C]`` holding each sequence's last W-1 inputs (oldest first), updated in place; optional int32
+    ``state_indices [N]`` selects the slots (negative: skip that sequence).  Returns ``y [N, C]``."""
+    _req(x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_cuda and x.stride(1) == 1, "x must be a bf16 CUDA tensor [N, C]")
+    N, Cn = x.shape
+    W = weight.shape[1]
+    _req(weight.dtype == torch.bfloat16 and tuple(weight.shape) == (Cn, W) and weight.device == x.device and 2 <= W <= 4,
+         f"weight must be a bf16 tensor [{Cn}, W] with W in 2..4 on {x.device}")
+    _req(Cn % 8 == 0, f"channels must be a multiple of 8, got {Cn}.")
+    _req(conv_state.dtype == torch.bfloat16 and conv_state.dim() == 3 and tuple(conv_state.shape[1:]) == (W - 1, Cn)
+         and conv_state.is_contiguous() and conv_state.device == x.device,
+         f"conv_state must be a contiguous bf16 tensor [slots, {W - 1}, {Cn}] on {x.device}")
+    if state_indices is not None:
+        _req(state_indices.dtype == torch.int32 and tuple(state_indices.shape) == (N,) and state_indices.device == x.device
+             and state_indices.is_contiguous(), f"state_indices must be a contiguous int32 tensor ({N},) on {x.device}")
+    else:
+        _req(conv_state.shape[0] >= N, "conv_state needs one slot per sequence when state_indices is not given")
+    weight = weight.contiguous()
+    if out is None:
+        out = torch.empty((N, Cn), dtype=torch.bfloat16, device=x.device)
+    _req(out.shape == x.shape and out.dtype == torch.bfloat16 and out.device == x.device and out.stride(1) == 1,
+         f"out must be a bf16 tensor of shape {tuple(x.shape)} on {x.device}")
+    a = _lib.ConvUpdateArgs()
+    a.struct_size = ctypes.sizeof(_lib.ConvUpdateArgs)
+    a.x, a.w, a.y, a.conv_state = x.data_ptr(), weight.data_ptr(), out.data_ptr(), conv_state.data_ptr()
+    a.bias = bias.contiguous().data_ptr() if bias is not None else None
+    a.state_indices = state_indices.data_ptr() if state_indices is not None else None
+    a.n_seqs, a.C, a.width, a.num_slots = N, Cn, W, conv_state.shape[0]
+    a.x_stride, a.y_stride = x.stride(0), out.stride(0)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().ave_gdn_conv1d_update(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "causal_conv1d_update")
     return out
 
 

@@ -381,7 +381,8 @@ def main():
             "config": workload_config(world),
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": 2 * args.steps, "clocks": clocks}
+            "gpu_launches": 15 * args.steps,  # five chunk ranges x (prep, scan, gated norm)
+            "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                         "frac": achieved / peaks["bf16_tflops"], "traffic": None,

@@ -162,6 +162,23 @@ typedef struct AveConvArgs {
 } AveConvArgs;
 int ave_gdn_conv1d_silu(const AveConvArgs* args, void* stream);
 
+/* Single-token form of the same convolution for decode: per sequence n, the last width-1 inputs live in slot
+ * state_indices[n] (or n) of a pool laid out [slots][width-1][C] bf16 (oldest first, channel-contiguous); the call
+ * computes y[n] = silu(bias + w . [history, x[n]]) and shifts x[n] into the history in place.  Negative index: skip. */
+typedef struct AveConvUpdateArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* x;              /* bf16 [n_seqs, C], row stride x_stride */
+  const void* w;              /* bf16 [C, width] */
+  const void* bias;           /* bf16 [C], optional */
+  void* y;                    /* bf16 [n_seqs, C], row stride y_stride */
+  void* conv_state;           /* bf16 [num_slots, width-1, C] */
+  const int32_t* state_indices; /* optional int32 [n_seqs] */
+  int32_t n_seqs, C, width, num_slots;
+  int64_t x_stride, y_stride;
+} AveConvUpdateArgs;
+int ave_gdn_conv1d_update(const AveConvUpdateArgs* args, void* stream);
+
 /* g = -exp(A_log[h]) * softplus(a + dt_bias[h]),  beta = sigmoid(b);  a,b bf16 [rows,Hv] (strided),
  * A_log,dt_bias fp32 [Hv];  g,beta fp32 [rows,Hv] contiguous. */
 typedef struct AveGateArgs {

@@ -106,3 +106,29 @@ def test_decode_full_size_step_properties(gdn, checker):
     untouched = torch.ones(512, dtype=torch.bool)
     untouched[inp.state_indices.long()] = False
     assert torch.equal(pool[untouched.cuda()], g.state_pool[untouched.cuda()])
+
+
+def test_prefill_into_pool_then_decode_matches_recurrence(gdn, checker):
+    """Continuous batching hand-off: the chunked prefill writes its final states straight into pool slots, decode
+    steps continue from those slots, and the whole thing equals one token recurrence over prompt + generated tokens."""
+    O, C = checker
+    Tp, Td, N, Hk, Hv, d = 150, 20, 2, 2, 4, 128
+    inp = synth.make_inputs(N, Tp + Td, Hk, Hv, d, d, seed=6, gate_scale=0.05)
+    g = dev(inp)
+    pool = torch.zeros(5, Hv, d, d, device="cuda")
+    idx = torch.tensor([3, 1], dtype=torch.int32, device="cuda")
+    # prefill the prompts as one packed batch
+    pk = lambda t: t[:, :Tp].reshape(1, N * Tp, *t.shape[2:]).contiguous()
+    cu = torch.tensor([0, Tp, 2 * Tp], dtype=torch.int32, device="cuda")
+    o_p, st = gdn.chunk_gated_delta_rule(pk(g.q), pk(g.k), pk(g.v), pk(g.g), pk(g.beta), initial_state=pool,
+                                         output_final_state=True, cu_seqlens=cu, state_indices=idx)
+    assert st.data_ptr() == pool.data_ptr()
+    outs = []
+    for t in range(Tp, Tp + Td):
+        o, _ = gdn.fused_recurrent_gated_delta_rule(g.q[:, t:t + 1], g.k[:, t:t + 1], g.v[:, t:t + 1], g.g[:, t:t + 1],
+                                                    g.beta[:, t:t + 1], initial_state=pool, state_indices=idx)
+        outs.append(o)
+    o_ref, s_ref = C.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale)
+    check_o(O, o_p.reshape(N, Tp, Hv, d), o_ref[:, :Tp])
+    check_o(O, torch.cat(outs, 1), o_ref[:, Tp:])
+    check_s(O, pool[idx.long()], s_ref)

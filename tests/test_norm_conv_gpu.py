@@ -79,3 +79,22 @@ def test_gate_beta(gdn, checker):
     g_ref, beta_ref = O.gate_beta(a_in, b_in, A_log, dt_bias)
     assert O.rel_l2(gg.cpu(), g_ref) < 1e-5 and O.rel_l2(beta.cpu(), beta_ref) < 1e-5
     assert (gg <= 0).all()
+
+
+def test_conv1d_update_matches_full_convolution(gdn, checker):
+    """T single-token updates from an empty history reproduce the causal convolution over the T tokens."""
+    O, _ = checker
+    g = torch.Generator().manual_seed(1)
+    N, T, Cn, W = 3, 9, 64, 4
+    x = torch.randn(N, T, Cn, generator=g).bfloat16()
+    w = (torch.randn(Cn, W, generator=g) / 2).bfloat16()
+    state = torch.zeros(5, W - 1, Cn, dtype=torch.bfloat16, device="cuda")
+    idx = torch.tensor([4, -1, 0], dtype=torch.int32, device="cuda")
+    ys = [gdn.causal_conv1d_update(x[:, t].cuda(), state, w.cuda(), state_indices=idx) for t in range(T)]
+    y = torch.stack(ys, 1)
+    ref = O.causal_conv1d_silu(x, w).bfloat16().float()
+    for n in (0, 2):
+        assert O.rel_l2(y[n].float().cpu(), ref[n]) < 1e-3
+    # the history now holds the last W-1 inputs, oldest first; untouched slots stay zero
+    assert torch.equal(state[4].cpu(), x[0, T - (W - 1):]) and torch.equal(state[0].cpu(), x[2, T - (W - 1):])
+    assert torch.count_nonzero(state[1:4]) == 0
