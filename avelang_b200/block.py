@@ -141,6 +141,29 @@ class GdnBlockShard:
         return full, peers
 
 
+class GdnBlockTP(GdnBlockShard):
+    """Tensor-parallel form of the block with the output projection: each rank multiplies its own heads' normalised
+    output by its column slice of ``w_out [hidden, Hv*dv]`` (row-parallel linear) and the partial results are summed
+    with one all-reduce, so no all-gather of head outputs is needed."""
+
+    def __init__(self, w_in, conv_w, A_log, dt_bias, norm_weight, w_out, *, Hk, Hv, dk, dv, rank=0, world=1, device="cuda"):
+        super().__init__(w_in, conv_w, A_log, dt_bias, norm_weight, Hk=Hk, Hv=Hv, dk=dk, dv=dv, rank=rank, world=world,
+                         device=device)
+        vh = self.shard.value_heads
+        self.w_out = w_out[:, vh.start * dv: vh.stop * dv].to(torch.bfloat16).to(device).contiguous()  # [hidden, hl*dv]
+
+    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None) -> torch.Tensor:
+        """Returns the block output after the output projection, ``[B, T, hidden]`` bf16, identical on every rank."""
+        from . import gemm
+        B, T, _ = x.shape
+        o = self.forward_local(x, cu_seqlens)                                   # [B, T, hl, dv]
+        part = gemm.gemm_pipeline_transposed_b(o.reshape(B * T, -1), self.w_out)  # [B*T, hidden], this rank's partial sum
+        if self.shard.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(part, group=group)
+        return part.reshape(B, T, -1)
+
+
 def gather_heads(o_local: torch.Tensor, world: int, group=None) -> torch.Tensor:
     """All-gather of [B, T, Hv/G, dv] head slices into [B, T, Hv, dv] (rank-major gather, then one transpose copy)."""
     if world == 1:
