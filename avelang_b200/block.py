@@ -141,6 +141,12 @@ class GdnBlockShard:
         return full, peers
 
 
+def output_projection_columns(shard: "HeadShard", dv: int) -> slice:
+    """Columns of the output-projection weight ``[hidden, Hv*dv]`` that multiply this shard's value heads."""
+    vh = shard.value_heads
+    return slice(vh.start * dv, vh.stop * dv)
+
+
 class GdnBlockTP(GdnBlockShard):
     """Tensor-parallel form of the block with the output projection: each rank multiplies its own heads' normalised
     output by its column slice of ``w_out [hidden, Hv*dv]`` (row-parallel linear) and the partial results are summed
@@ -149,8 +155,8 @@ class GdnBlockTP(GdnBlockShard):
     def __init__(self, w_in, conv_w, A_log, dt_bias, norm_weight, w_out, *, Hk, Hv, dk, dv, rank=0, world=1, device="cuda"):
         super().__init__(w_in, conv_w, A_log, dt_bias, norm_weight, Hk=Hk, Hv=Hv, dk=dk, dv=dv, rank=rank, world=world,
                          device=device)
-        vh = self.shard.value_heads
-        self.w_out = w_out[:, vh.start * dv: vh.stop * dv].to(torch.bfloat16).to(device).contiguous()  # [hidden, hl*dv]
+        cols = output_projection_columns(self.shard, dv)
+        self.w_out = w_out[:, cols].to(torch.bfloat16).to(device).contiguous()  # [hidden, hl*dv]
 
     def forward(self, x: torch.Tensor, cu_seqlens=None, group=None) -> torch.Tensor:
         """Returns the block output after the output projection, ``[B, T, hidden]`` bf16, identical on every rank."""

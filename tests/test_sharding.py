@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from avelang_b200.block import HeadShard, gather_heads, projection_rows
+from avelang_b200.block import HeadShard, gather_heads, output_projection_columns, projection_rows
 
 
 def test_head_shards_partition_all_heads():
@@ -54,4 +54,27 @@ def test_gather_heads_two_gloo_ranks():
     mgr = mp.Manager()
     out = mgr.dict()
     mp.spawn(_rank_main, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert dict(out) == {0: True, 1: True}
+
+
+def _rank_out_proj(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        Hv, dv, hidden = 4, 8, 16
+        heads = torch.randn(6, Hv, dv, generator=g)
+        w_out = torch.randn(hidden, Hv * dv, generator=g)
+        shard = HeadShard(rank, world, 2, Hv)
+        part = heads[:, shard.value_heads].reshape(6, -1) @ w_out[:, output_projection_columns(shard, dv)].T
+        dist.all_reduce(part)
+        out[rank] = bool(torch.allclose(part, heads.reshape(6, -1) @ w_out.T, atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_parallel_output_projection_two_gloo_ranks():
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_rank_out_proj, args=(2, _free_port(), out), nprocs=2, join=True)
     assert dict(out) == {0: True, 1: True}
