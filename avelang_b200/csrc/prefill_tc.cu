@@ -29,8 +29,8 @@ constexpr int REC_P = C * C * 2;       // one bf16 [64][64] tile
 constexpr int SCAL_FLOATS = 3 * C;     // qs[64] ks[64] decay(+pad)
 
 struct PrepOut {
-  __nv_bfloat16 *w_hi, *w_lo, *p_hi, *p_lo;
-  float *u, *scal;
+  __nv_bfloat16 *w_hi, *w_lo, *p_hi, *p_lo, *tu_hi, *tu_lo;
+  float *scal;
 };
 
 struct ChunkRef { int n, b, t0, len, cis; bool ok; };  // cis: index of the chunk inside its sequence
@@ -84,7 +84,7 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define TL_START(slot) do { if (threadIdx.x == 0) atomicMin(&g_tl[2 * (slot)], gtime()); } while (0)
 #define TL_END(slot) do { if (threadIdx.x == 0) atomicMax(&g_tl[2 * (slot) + 1], gtime()); } while (0)
 __device__ long long g_trace[16 * 1024];
-#define PTRACE(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0) g_trace[16 * 1000 + (slot)] = clock64(); } while (0)
+#define PTRACE(slot) do { if (blockIdx.x == 300 && blockIdx.y == 7 && threadIdx.x == 0) g_trace[16 * 1000 + (slot)] = clock64(); } while (0)
 #define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(slot, c) do {} while (0)
@@ -94,7 +94,7 @@ __device__ long long g_trace[16 * 1024];
 #endif
 
 struct GdnMaps {
-  CUtensorMap q, k, v, w_hi, w_lo, p_hi, p_lo;
+  CUtensorMap q, k, v, p_hi, p_lo, tu_hi, tu_lo;
 };
 
 // ------------------------------------------------------------------------------------------------ pass 1
@@ -158,28 +158,28 @@ __device__ __forceinline__ void block_store(float* __restrict__ dst, const float
 }
 
 constexpr int PREP_THREADS = 256;
-constexpr int U_LD = 68;                              // row stride (floats) of U^T: 16-byte rows, conflict-free float4 reads
-constexpr int U_REC_BYTES = D * U_LD * 4;             // 34816
-// Regions are reused as their contents die, which keeps a CTA under 70 KB so that three fit on an SM:
-//   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   the Q halves later hold Tw hi / Tw lo; after the W MMA the region is store staging
-//   PP_R1  E, E^2, E^3 block scratch       later Tu hi | Tu lo, then store staging
-//   PP_R2  A -> T blocks and D^-1 blocks   later the V tile (loaded only once the blocks are dead)
+// Regions are reused as their contents die, which keeps a CTA at 52 KB so that four fit on an SM:
+//   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   the Q halves hold the E, E^2, E^3 block scratch once the Gram MMA is done, then
+//                                        Tw hi / Tw lo; after the W MMA the region is the store image of W^T hi | W^T lo
+//   PP_R2  A -> T blocks and D^-1 blocks
 constexpr int PP_KQ = 0, PP_TWH = PP_KQ + 8192, PP_TWL = PP_KQ + 24576,
-              PP_R1 = 32768, PP_TUH = PP_R1, PP_TUL = PP_R1 + 8192,
-              PP_R2 = 49152, PP_A = PP_R2, PP_DI = PP_A + 10 * BLK_FLOATS * 4, PP_V = PP_R2,
+              PP_WHI = PP_KQ, PP_WLO = PP_KQ + 16384,
+              PP_R2 = 32768, PP_A = PP_R2, PP_DI = PP_A + 10 * BLK_FLOATS * 4,
               PP_SC = PP_R2 + 18432, PP_BARS = PP_SC + 4 * C * 4;
-constexpr int PP_E = PP_R1, PP_E2 = PP_E + 6 * BLK_FLOATS * 4, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
-static_assert(PP_E3 + BLK_FLOATS * 4 <= PP_R1 + 16384, "block scratch must fit inside its region");
+constexpr int PP_E = PP_TWH, PP_E2 = PP_TWL, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
+static_assert(6 * BLK_FLOATS * 4 <= 8192 && 4 * BLK_FLOATS * 4 <= 8192, "block scratch must fit inside the Q halves");
 static_assert(PP_DI + 4 * BLK_FLOATS * 4 <= PP_R2 + 18432, "T and D^-1 blocks must fit inside their region");
 constexpr size_t PREP_SMEM = PP_BARS + 64 + 1024;
-constexpr uint32_t PT_GRAM = 0, PT_W = 0, PT_U = 64;    // TMEM columns (128 allocated; W^T reuses the Gram columns)
+constexpr uint32_t PT_GRAM = 0, PT_W = 0;               // TMEM columns (64 allocated; W^T reuses the Gram columns)
 
 // Pass 1 per (chunk, value head):
 //   tensor cores: [K; Q] K^T                                   -> A (strict lower, gated) and P (lower, gated)
-//   CUDA cores  : T = (I + A)^-1 by forward substitution (4 threads per column, rows interleaved mod 4)
-//   tensor cores: W^T = K^T (T diag(beta e^b))^T,  U^T = V^T (T diag(beta))^T   (M = 128 = d_k / d_v, N = 64 tokens)
-// W^T leaves as bf16 hi + lo [128][64] (the scan reads it as an MN-major B operand), U^T as fp32 [128][68].
-__global__ void __launch_bounds__(PREP_THREADS, 3)
+//   CUDA cores  : T = (I + A)^-1 by 16x16 blocks (warp-level tf32 MMAs for the block products)
+//   tensor cores: W^T = K^T (T diag(beta e^b))^T   (M = 128 = d_k, N = 64 tokens)
+// W^T leaves as bf16 hi + lo, as the 128-byte-swizzled shared-memory image of a [128][64] tile (one bulk copy out here,
+// one bulk copy in by the scan, which reads it as an MN-major B operand); Tu = T diag(beta) leaves as bf16 hi + lo
+// [64][64] row-major: the scan forms U^T = V^T Tu^T itself, straight into its Vn accumulator.
+__global__ void __launch_bounds__(PREP_THREADS, 4)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out,
                   int seg_c0, int seg_n, int compact_grid) {
   extern __shared__ uint8_t smem_raw[];
@@ -197,7 +197,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   uint64_t* tma_bar = bars;
   uint64_t* mma_bar = bars + 1;
   uint64_t* mma2_bar = bars + 2;   // W^T accumulated
-  uint64_t* mma3_bar = bars + 3;   // U^T accumulated
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -214,7 +213,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   const ChunkRef cr = find_chunk(a, chunk_start, c);
   if (!cr.ok || cr.cis < seg_c0 || cr.cis >= seg_c0 + seg_n) return;  // not in this launch's range of chunks
-  TL_START(compact_grid ? seg_c0 / seg_n : 0);
+  TL_START(compact_grid ? (seg_c0 + seg_n - 1) / seg_n : 0);
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
@@ -223,7 +222,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::mbar_init(tma_bar, 1);
     tc::mbar_init(mma_bar, 1);
     tc::mbar_init(mma2_bar, 1);
-    tc::mbar_init(mma3_bar, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::mbar_expect_tx(tma_bar, 32768);
@@ -232,16 +230,19 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::tma_load_4d(smem + PP_KQ + 16384, &maps.k, tma_bar, 64, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 24576, &maps.q, tma_bar, 64, hk, cr.t0, cr.b);
   }
-  if (warp == 2) tc::tmem_alloc(tmem_slot, 128);
+  PTRACE(13);
+  if (warp == 2) tc::tmem_alloc(tmem_slot, 64);
   if (tid < C) {
     const bool valid = tid < cr.len;
     const int64_t off = cr.b * a.g_stride_b + (int64_t)(cr.t0 + tid) * a.g_stride_t + h;
     bs[tid] = valid ? a.g[off] : 0.f;
     betas[tid] = valid ? a.beta[off] : 0.f;
   }
+  PTRACE(14);
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
+  PTRACE(15);
   const uint32_t tm = *tmem_slot;
   if (warp == 1) {  // in-chunk cumulative gate: inclusive scan of 64 values by one warp
     float v0 = bs[lane], v1 = bs[32 + lane];
@@ -432,11 +433,14 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   __syncthreads();
   PTRACE(7);
-  // Tw = T diag(beta e^b kn), Tu = T diag(beta): bf16 hi + lo K-major tiles [i][j], 128-byte swizzle, two columns per store
+  // Tw = T diag(beta e^b kn) as bf16 hi + lo K-major tiles [i][j] with the 128-byte swizzle (B operand of the W MMA);
+  // Tu = T diag(beta) as bf16 hi + lo rows straight to scratch (a warp writes one full 128-byte row per store)
   {
     const int j = (tid & 31) * 2;  // this thread's column pair; rows (tid >> 5) + 8 q
     const float fu0 = betas[j], fu1 = betas[j + 1], fw0 = fwv[j], fw1 = fwv[j + 1];
     const int cb = j >> 4;
+    uint32_t* guh = reinterpret_cast<uint32_t*>(out.tu_hi + rec * (C * C)) + (tid & 31);
+    uint32_t* gul = reinterpret_cast<uint32_t*>(out.tu_lo + rec * (C * C)) + (tid & 31);
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const int i = (tid >> 5) + 8 * q;
@@ -453,20 +457,15 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       *reinterpret_cast<uint32_t*>(smem + PP_TWH + off) = wh;
       *reinterpret_cast<uint32_t*>(smem + PP_TWL + off) =
           pack_bf16x2(w0 - __uint_as_float(wh << 16), w1 - __uint_as_float(wh & 0xffff0000u));
-      *reinterpret_cast<uint32_t*>(smem + PP_TUH + off) = uh;
-      *reinterpret_cast<uint32_t*>(smem + PP_TUL + off) =
-          pack_bf16x2(u0 - __uint_as_float(uh << 16), u1 - __uint_as_float(uh & 0xffff0000u));
+      if (ok) {
+        guh[i * (C / 2)] = uh;
+        gul[i * (C / 2)] = pack_bf16x2(u0 - __uint_as_float(uh << 16), u1 - __uint_as_float(uh & 0xffff0000u));
+      }
     }
   }
   tc::fence_proxy_async_smem();
   __syncthreads();
-  // The T and D^-1 blocks are dead now: the V tile takes their place while W^T is being formed.
-  if (tid == 0 && ok) {
-    tc::mbar_expect_tx(tma_bar, 16384);
-    tc::tma_load_4d(smem + PP_V, &maps.v, tma_bar, 0, h, cr.t0, cr.b);
-    tc::tma_load_4d(smem + PP_V + 8192, &maps.v, tma_bar, 64, h, cr.t0, cr.b);
-  }
-  constexpr uint32_t idesc_wu = tc::idesc_f16(128, 64, 1, 1, true, false);  // A MN-major (token rows), B K-major
+  constexpr uint32_t idesc_w = tc::idesc_f16(128, 64, 1, 1, true, false);  // A MN-major (token rows), B K-major
   if (warp == 0) {
     const bool leader = tc::elect_one();
     if (ok && leader) {
@@ -476,108 +475,60 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
         const uint32_t tw = tc::smem_u32(smem + (t ? PP_TWL : PP_TWH));
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // K halves sit 16384 bytes apart (the Q halves' slots lie between them)
-          tc::mma_ss(tm + PT_W, tc::smem_desc_sw128(kbase + k * 2048, 16384, 1024), tc::smem_desc_sw128(tw + k * 32, 16, 1024), idesc_wu,
+          tc::mma_ss(tm + PT_W, tc::smem_desc_sw128(kbase + k * 2048, 16384, 1024), tc::smem_desc_sw128(tw + k * 32, 16, 1024), idesc_w,
                      (t | k) != 0 ? 1u : 0u);
       }
       tc::mma_commit(mma2_bar);
     }
     __syncwarp();
-  } else if (warp == 4) {
-    const bool v_ok = ok && tc::mbar_wait(tma_bar, 1, abort_flag);
-    tc::tc_fence_after_sync();
-    const bool leader = tc::elect_one();
-    if (v_ok && leader) {
-      const uint32_t vbase = tc::smem_u32(smem + PP_V);
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const uint32_t tu = tc::smem_u32(smem + (t ? PP_TUL : PP_TUH));
-#pragma unroll
-        for (int k = 0; k < 4; ++k)  // V halves are adjacent, 8192 bytes apart
-          tc::mma_ss(tm + PT_U, tc::smem_desc_sw128(vbase + k * 2048, 8192, 1024), tc::smem_desc_sw128(tu + k * 32, 16, 1024), idesc_wu,
-                     (t | k) != 0 ? 1u : 0u);
-      }
-      tc::mma_commit(mma3_bar);
-    }
-    __syncwarp();
   }
   PTRACE(8);
-  // warps 0..3 turn W^T into bf16 hi + lo as soon as it is complete; warps 4..7 wait for U^T (issued after W^T)
   ok = ok && tc::mbar_wait(mma2_bar, 0, abort_flag);
-  if (warp >= 4) ok = ok && tc::mbar_wait(mma3_bar, 0, abort_flag);  // a different thread issued U^T: wait for both
   PTRACE(9);
   tc::tc_fence_after_sync();
   {
-    const int quarter = warp & 3;
-    const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
-    // Each lane owns one output row.  A direct store would scatter 32 rows per instruction, so rows are transposed
-    // through a per-warp staging area (the K/Q/V tiles are dead by now) with an XOR swizzle on 16-byte pieces and
-    // written back as fully coalesced 512-byte stores.
-    if (warp < 4) {
-      uint4* st = reinterpret_cast<uint4*>(smem + PP_KQ + warp * 4096);        // 32 rows x 128 B
-      uint4* gh = reinterpret_cast<uint4*>(out.w_hi + rec * (C * D) + (quarter * 32) * C);
-      uint4* gl = reinterpret_cast<uint4*>(out.w_lo + rec * (C * D) + (quarter * 32) * C);
-      uint32_t hi[32], lo[32];
+    // Each lane owns one row of W^T (a d_k index) and each warp half of its 64 tokens.  The K, Q and Tw tiles are dead
+    // now; the bf16 hi and lo rows are written over them in the 128-byte-swizzled tile layout the scan's MMA reads, so
+    // that the tile leaves with one bulk copy and arrives in the scan's shared memory with another, unchanged.
+    const int quarter = warp & 3, colhalf = warp >> 2;
+    const int r = quarter * 32 + lane;
+    uint32_t acc[32];
+    tc::tmem_ld32(tm + PT_W + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
+    tc::tmem_ld_wait();
+    uint4* ih = reinterpret_cast<uint4*>(smem + PP_WHI + r * 128);
+    uint4* il = reinterpret_cast<uint4*>(smem + PP_WLO + r * 128);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t acc[32];
-        tc::tmem_ld32(lane_addr + PT_W + 32 * half, acc);
-        tc::tmem_ld_wait();
+    for (int p4 = 0; p4 < 4; ++p4) {
+      uint32_t hi[4], lo[4];
 #pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          const float v0 = __uint_as_float(acc[2 * w]), v1 = __uint_as_float(acc[2 * w + 1]);
-          hi[16 * half + w] = pack_bf16x2(v0, v1);
-          lo[16 * half + w] = pack_bf16x2(v0 - __uint_as_float(hi[16 * half + w] << 16), v1 - __uint_as_float(hi[16 * half + w] & 0xffff0000u));
-        }
+      for (int w = 0; w < 4; ++w) {
+        const float v0 = __uint_as_float(acc[8 * p4 + 2 * w]), v1 = __uint_as_float(acc[8 * p4 + 2 * w + 1]);
+        hi[w] = pack_bf16x2(v0, v1);
+        lo[w] = pack_bf16x2(v0 - __uint_as_float(hi[w] << 16), v1 - __uint_as_float(hi[w] & 0xffff0000u));
       }
-      PTRACE(11);
-#pragma unroll
-      for (int pass = 0; pass < 2; ++pass) {
-        const uint32_t* src = pass ? lo : hi;
-#pragma unroll
-        for (int p8 = 0; p8 < 8; ++p8) st[lane * 8 + (p8 ^ (lane & 7))] = make_uint4(src[4 * p8], src[4 * p8 + 1], src[4 * p8 + 2], src[4 * p8 + 3]);
-        __syncwarp();
-        if (ok) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int m = 32 * k + lane, row = m >> 3, piece = m & 7;
-            (pass ? gl : gh)[m] = st[row * 8 + (piece ^ (row & 7))];
-          }
-        }
-        __syncwarp();
-      }
-      PTRACE(12);
-    } else {
-      // K_h1 / Tw lo are dead once W^T is complete, the Tu tiles once U^T is complete (and U^T is issued after W^T)
-      uint4* st = reinterpret_cast<uint4*>(smem + (warp < 6 ? PP_KQ + 16384 + (warp - 4) * 8192 : PP_R1 + (warp - 6) * 8192));  // 32 rows x 256 B
-      float* gu = out.u + rec * (D * U_LD) + (quarter * 32) * U_LD;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t acc[32];
-        tc::tmem_ld32(lane_addr + PT_U + 32 * half, acc);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int p8 = 0; p8 < 8; ++p8)
-          st[lane * 16 + ((8 * half + p8) ^ (lane & 7))] = make_uint4(acc[4 * p8], acc[4 * p8 + 1], acc[4 * p8 + 2], acc[4 * p8 + 3]);
-      }
-      __syncwarp();
-      if (ok) {
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const int m = 32 * k + lane, row = m >> 4, piece = m & 15;
-          *reinterpret_cast<uint4*>(gu + row * U_LD + piece * 4) = st[row * 16 + (piece ^ (row & 7))];
-        }
-      }
+      const int piece = (4 * colhalf + p4) ^ (r & 7);
+      ih[piece] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      il[piece] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
   }
+  PTRACE(11);
+  tc::fence_proxy_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
+  if (tid == 0 && ok) {
+    tc::bulk_store(out.w_hi + rec * (C * D), smem + PP_WHI, REC_W);
+    tc::bulk_store(out.w_lo + rec * (C * D), smem + PP_WLO, REC_W);
+    tc::bulk_commit();
+    tc::bulk_wait_read<0>();  // shared memory must stay intact until the copies have read it
+  }
+  PTRACE(12);
   if (warp == 2) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tm, 128);
+    tc::tmem_dealloc(tm, 64);
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
   PTRACE(10);
-  TL_END(compact_grid ? seg_c0 / seg_n : 0);
+  TL_END(compact_grid ? (seg_c0 + seg_n - 1) / seg_n : 0);
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
@@ -597,9 +548,10 @@ constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
 constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
 constexpr int OFF_SCAL = 2 * STAGE;                  // 4 x [qs | ks | decay]: a deeper ring than the tile stages, because
                                                      // the output warps read qs up to a chunk after the stage is recycled
-constexpr int OFF_U = OFF_SCAL + 4 * SCAL_BYTES;     // fp32 [64][128], single buffer
-constexpr int U_BYTES = U_REC_BYTES;
-constexpr int OFF_BARS = OFF_U + U_BYTES;
+constexpr int OFF_VT = OFF_SCAL + 4 * SCAL_BYTES;    // single buffer: V tile (two 64-feature halves) | Tu hi | Tu lo
+constexpr int VT_V = 0, VT_TUH = 16384, VT_TUL = 24576, VT_BYTES = 32768;
+static_assert(OFF_VT % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+constexpr int OFF_BARS = OFF_VT + VT_BYTES;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
 // TMEM columns
 constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO = 160, TM_VDHI = 192, TM_VDLO = 224,
@@ -638,11 +590,11 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
-                     const float* __restrict__ u_ws, const float* __restrict__ scal_ws, float* __restrict__ o_f32,
+                     const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
+                     const float* __restrict__ scal_ws, float* __restrict__ o_f32,
                      float* __restrict__ carry, int seg_c0, int seg_n) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const float* u_s = reinterpret_cast<const float*>(smem + OFF_U);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
   uint64_t* full = bars;          // [2] stage landed
   uint64_t* empty = bars + 2;     // [2] stage consumed
@@ -652,8 +604,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   uint64_t* dh_full = bars + 7;   // state increment accumulated
   uint64_t* o_full = bars + 8;    // both output accumulators complete
   uint64_t* o_empty = bars + 9;   // output accumulators drained
-  uint64_t* u_full = bars + 10;
-  uint64_t* u_empty = bars + 11;
+  uint64_t* u_full = bars + 10;   // V and Tu tiles landed
+  uint64_t* u_empty = bars + 11;  // the U^T MMAs that read them are complete
   uint64_t* chain_bar = bars + 12;
   uint64_t* vd_ready = bars + 14; // Vd hi+lo written to TMEM (the state update needs nothing else)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
@@ -709,7 +661,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::mbar_init(&empty[0], 9); tc::mbar_init(&empty[1], 9);
     tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
     tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
-    tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 8);
+    tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 1);
     tc::mbar_init(chain_bar, 8); tc::mbar_init(vd_ready, 8);
     *abort_flag = 0;
     tc::fence_barrier_init();
@@ -719,7 +671,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  TL_START(8 + (seg_n < (1 << 20) ? seg_c0 / seg_n : 0));
+  TL_START(8 + (seg_n < (1 << 20) ? (seg_c0 + seg_n - 1) / seg_n : 0));
 
   if (warp < 4) {
   tc::reg_set<REGS_CTRL, 128>();
@@ -735,8 +687,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         const int row = (int)(rec * C);
         const int tok = sp.t0 + c * C;
         tc::mbar_expect_tx(&full[s], STAGE_TX);
-        tc::tma_load_2d(st + ST_WHI, &maps.w_hi, &full[s], 0, 2 * row);  // W^T tile: 128 d_k rows of 64 tokens
-        tc::tma_load_2d(st + ST_WLO, &maps.w_lo, &full[s], 0, 2 * row);
+        tc::bulk_load(st + ST_WHI, w_hi_ws + rec * (C * D), REC_W, &full[s]);  // W^T tile images: 128 d_k rows of 64 tokens
+        tc::bulk_load(st + ST_WLO, w_lo_ws + rec * (C * D), REC_W, &full[s]);
         tc::tma_load_4d(st + ST_Q, &maps.q, &full[s], 0, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_Q + 8192, &maps.q, &full[s], 64, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_K, &maps.k, &full[s], 0, hk, tok, sp.b);
@@ -744,10 +696,14 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tma_load_2d(st + ST_PHI, &maps.p_hi, &full[s], 0, row);
         tc::tma_load_2d(st + ST_PLO, &maps.p_lo, &full[s], 0, row);
         tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
-        // U of chunk c replaces U of chunk c-1 once the chain epilogue has consumed it
+        // V and Tu of chunk c replace those of chunk c-1 once the U^T MMAs of chunk c-1 have read them
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
-        tc::mbar_expect_tx(u_full, U_BYTES);
-        tc::bulk_load(smem + OFF_U, u_ws + rec * (D * U_LD), U_BYTES, u_full);
+        uint8_t* vt = smem + OFF_VT;
+        tc::mbar_expect_tx(u_full, VT_BYTES);
+        tc::tma_load_4d(vt + VT_V, &maps.v, u_full, 0, h, tok, sp.b);
+        tc::tma_load_4d(vt + VT_V + 8192, &maps.v, u_full, 64, h, tok, sp.b);
+        tc::tma_load_2d(vt + VT_TUH, &maps.tu_hi, u_full, 0, row);
+        tc::tma_load_2d(vt + VT_TUL, &maps.tu_lo, u_full, 0, row);
       }
     }
   } else if (warp == 1) {
@@ -756,18 +712,35 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, true, true, false);    // negated A, B = W^T read MN-major
     constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
     constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
+    constexpr uint32_t id_u = tc::idesc_f16(128, 64, 1, 1, true, false);                  // A = V tile read MN-major
+    const uint32_t vtb = tc::smem_u32(smem + OFF_VT);
     for (int c = 0; c < n_chunks; ++c) {
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const uint32_t sb = tc::smem_u32(smem + s * STAGE);
       if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) break;
       TRACE(0, c);
+      // U^T = V^T (Tu_hi + Tu_lo)^T opens the Vn^T accumulator; it does not depend on the state, so it runs while the
+      // chain epilogue is still re-packing H.  The previous chunk's O2 MMAs, which read these columns, were issued earlier
+      // by this thread and complete first.
+      if (!tc::mbar_wait(u_full, cp, abort_flag)) break;
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 16 tokens per step: V rows 2048 bytes apart, feature halves 8192 bytes apart
+            tc::mma_ss(tm + TM_VN, tc::smem_desc_sw128(vtb + VT_V + k * 2048, 8192, 1024),
+                       tc::smem_desc_sw128(vtb + (t ? VT_TUL : VT_TUH) + k * 32, 16, 1024), id_u, (t | k) != 0 ? 1u : 0u);
+        tc::mma_commit(u_empty);
+      }
+      __syncwarp();
       if (!tc::mbar_wait(h_ready, cp, abort_flag)) break;
       TRACE(1, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
-        // Vn^T accumulator = -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); W^T is one [128 d_k][64 token] tile, 16 d_k rows per step
-        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 2048, 0, 16, id_vn, 8, false);
+        // Vn^T += -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); W^T is one [128 d_k][64 token] tile, 16 d_k rows per step
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
         issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 2048, 0, 16, id_vn, 8, true);
         issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
         tc::mma_commit(vn_full);
@@ -850,7 +823,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
       if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
-      if (!tc::mbar_wait(u_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(6, c);
       if (!tc::mbar_wait(vn_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(7, c);
@@ -859,16 +831,9 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         uint32_t acc[32];
         tc::tmem_ld32(lane_addr + TM_VN + 32 * grp, acc);
         float2 v[16];
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          const float4 uq = *reinterpret_cast<const float4*>(u_s + d * U_LD + 32 * grp + 4 * j4);
-          v[2 * j4] = make_float2(uq.x, uq.y); v[2 * j4 + 1] = make_float2(uq.z, uq.w);
-        }
         tc::tmem_ld_wait();
 #pragma unroll
-        for (int w = 0; w < 16; ++w) v[w] = __fadd2_rn(v[w], make_float2(__uint_as_float(acc[2 * w]), __uint_as_float(acc[2 * w + 1])));
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(u_empty);
+        for (int w = 0; w < 16; ++w) v[w] = make_float2(__uint_as_float(acc[2 * w]), __uint_as_float(acc[2 * w + 1]));
         {  // Vd first: its columns alias nothing, and the state update waits only for it
           uint32_t dh[16], dl[16];
 #pragma unroll
@@ -999,11 +964,11 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 512);
   }
-  TL_END(8 + (seg_n < (1 << 20) ? seg_c0 / seg_n : 0));
+  TL_END(8 + (seg_n < (1 << 20) ? (seg_c0 + seg_n - 1) / seg_n : 0));
 }
 
 struct WsLayout {
-  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, u, scal, o_f32, carry, total;
+  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, carry, total;
   int64_t chunks;
   int segments;        // chunk ranges per sequence handled by separate launches
   int seg_begin[9];    // range i covers chunks [seg_begin[i], seg_begin[i+1]) of every sequence
@@ -1020,7 +985,8 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   L.w_lo = off; off = up(off + recs * REC_W);
   L.p_hi = off; off = up(off + recs * REC_P);
   L.p_lo = off; off = up(off + recs * REC_P);
-  L.u = off; off = up(off + recs * (size_t)U_REC_BYTES);
+  L.tu_hi = off; off = up(off + recs * REC_P);
+  L.tu_lo = off; off = up(off + recs * REC_P);
   L.scal = off; off = up(off + recs * (size_t)(SCAL_FLOATS * 4));
   L.o_f32 = off;
   if (a.z != nullptr) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // un-normalised output for the gated norm
@@ -1122,17 +1088,18 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
   po.w_lo = reinterpret_cast<__nv_bfloat16*>(ws + L.w_lo);
   po.p_hi = reinterpret_cast<__nv_bfloat16*>(ws + L.p_hi);
   po.p_lo = reinterpret_cast<__nv_bfloat16*>(ws + L.p_lo);
-  po.u = reinterpret_cast<float*>(ws + L.u);
+  po.tu_hi = reinterpret_cast<__nv_bfloat16*>(ws + L.tu_hi);
+  po.tu_lo = reinterpret_cast<__nv_bfloat16*>(ws + L.tu_lo);
   po.scal = reinterpret_cast<float*>(ws + L.scal);
 
   GdnMaps maps;
   const uint64_t rows = (uint64_t)L.chunks * a.Hv * C;
   {
-    const uint64_t dw[2] = {C, 2 * rows}, sw[2] = {2, C * 2}, dp[2] = {C, rows}, spp[2] = {2, C * 2};
-    const uint32_t box[2] = {64, 64}, boxw[2] = {64, 128};
+    const uint64_t dp[2] = {C, rows}, spp[2] = {2, C * 2};
+    const uint32_t box[2] = {64, 64};
     int rc;
-    if ((rc = make_tmap(&maps.w_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_hi, 2, dw, sw, boxw, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    if ((rc = make_tmap(&maps.w_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.w_lo, 2, dw, sw, boxw, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&maps.tu_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&maps.tu_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.p_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.p_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     const uint32_t box4[4] = {64, 1, 64, 1};
@@ -1167,7 +1134,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry, 0, big);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.scal, o_f32, carry, 0, big);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
     // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1186,7 +1153,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.u, po.scal, o_f32, carry, c0, cn);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.scal, o_f32, carry, c0, cn);
       AVE_CUDA_TRY(cudaGetLastError());
       if (norm_per_range) {
         AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
@@ -1220,7 +1187,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
 // every GPU that loads the library carries until the process exits.
 namespace ave {
 int validate_prefill_args(const AveGdnArgs* a);
-constexpr size_t kStaticScratchBytes = AVE_GDN_NOALLOC_SCRATCH_BYTES;  // 64 MiB: about 790 chunk-heads of d = 128
+constexpr size_t kStaticScratchBytes = AVE_GDN_NOALLOC_SCRATCH_BYTES;  // 64 MiB: about 1000 chunk-heads of d = 128
 }
 static __device__ __align__(256) unsigned char g_static_prefill_scratch[ave::kStaticScratchBytes];
 

@@ -353,6 +353,12 @@ def profile_case(name: str):
         inp = synth.config1(T=2048).to("cuda")
         for _ in range(2):
             gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, output_final_state=True, z=inp.z)
+    elif name == "varlen32k":
+        # throughput regime in the small: 64 packed sequences, about 550 chunks x 32 heads, 1.5 GB of scratch
+        inp = synth.config3(total=32768, lo=128, hi=2048).to("cuda")
+        for _ in range(2):
+            gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, initial_state=inp.initial_state,
+                                       output_final_state=True, cu_seqlens=inp.cu_seqlens)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     torch.cuda.synchronize()
@@ -369,7 +375,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block"],
                     help="prefill (default, the headline line), varlen (head-sharded packed prefill) or block")
-    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048"],
+    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k"],
                     help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
     if args.profile_case:

@@ -105,7 +105,7 @@ size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args);
  * that has handed all of HBM to its paged pools, a plug-in callback limited to pre-registered buffers, a path where
  * allocator calls are forbidden): `workspace` / `workspace_bytes` are ignored and the scratch is a fixed 64 MiB
  * array inside the library (AVE_GDN_NOALLOC_SCRATCH_BYTES), held by every GPU that loads the library until the
- * process exits.  Requests needing more scratch than that, i.e. more than about 790 (chunk, value head) pairs, return
+ * process exits.  Requests needing more scratch than that, i.e. more than about 1000 (chunk, value head) pairs, return
  * AVE_GDN_WORKSPACE_TOO_SMALL; only dk = dv = 128 is served.  Calls no cudaMalloc/cudaFree or other allocating routine.
  * The first call on a device looks up the array's device address and should be made outside stream capture.  All
  * calls share the one array: calls that overlap on the GPU (different streams) race; nothing needs clearing between
