@@ -94,7 +94,7 @@ __device__ long long g_trace[16 * 1024];
 #endif
 
 struct GdnMaps {
-  CUtensorMap q, k, v, p_hi, p_lo, tu_hi, tu_lo;
+  CUtensorMap q, k, v, tu_hi, tu_lo;
 };
 
 // ------------------------------------------------------------------------------------------------ pass 1
@@ -159,13 +159,15 @@ __device__ __forceinline__ void block_store(float* __restrict__ dst, const float
 
 constexpr int PREP_THREADS = 256;
 // Regions are reused as their contents die, which keeps a CTA at 52 KB so that four fit on an SM:
-//   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   the Q halves hold the E, E^2, E^3 block scratch once the Gram MMA is done, then
-//                                        Tw hi / Tw lo; after the W MMA the region is the store image of W^T hi | W^T lo
+//   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   once the Gram MMA is done the Q halves hold the store images of P hi / P lo, then
+//                                        the E, E^2, E^3 block scratch, then Tw hi / Tw lo; after the W MMA the whole
+//                                        region is the store image of W^T hi | W^T lo
 //   PP_R2  A -> T blocks and D^-1 blocks
 constexpr int PP_KQ = 0, PP_TWH = PP_KQ + 8192, PP_TWL = PP_KQ + 24576,
               PP_WHI = PP_KQ, PP_WLO = PP_KQ + 16384,
               PP_R2 = 32768, PP_A = PP_R2, PP_DI = PP_A + 10 * BLK_FLOATS * 4,
               PP_SC = PP_R2 + 18432, PP_BARS = PP_SC + 4 * C * 4;
+constexpr int PP_PHI = PP_TWH, PP_PLO = PP_TWL;        // P hi / P lo tile images, before the block scratch
 constexpr int PP_E = PP_TWH, PP_E2 = PP_TWL, PP_E3 = PP_E2 + 3 * BLK_FLOATS * 4;
 static_assert(6 * BLK_FLOATS * 4 <= 8192 && 4 * BLK_FLOATS * 4 <= 8192, "block scratch must fit inside the Q halves");
 static_assert(PP_DI + 4 * BLK_FLOATS * 4 <= PP_R2 + 18432, "T and D^-1 blocks must fit inside their region");
@@ -343,16 +345,25 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
         ph[w] = pack_bf16x2(p0, p1);
         pl[w] = pack_bf16x2(p0 - __uint_as_float(ph[w] << 16), p1 - __uint_as_float(ph[w] & 0xffff0000u));
       }
-      uint4* dh = reinterpret_cast<uint4*>(out.p_hi + rec * (C * C) + i * C + 32 * colhalf);
-      uint4* dl = reinterpret_cast<uint4*>(out.p_lo + rec * (C * C) + i * C + 32 * colhalf);
+      // the Q halves are dead (the Gram MMA is complete): they take the swizzled tile images of P hi and P lo, which
+      // leave with one bulk copy each
+      uint4* ih = reinterpret_cast<uint4*>(smem + PP_PHI + i * 128);
+      uint4* il = reinterpret_cast<uint4*>(smem + PP_PLO + i * 128);
 #pragma unroll
       for (int v4 = 0; v4 < 4; ++v4) {
-        dh[v4] = make_uint4(ph[4 * v4], ph[4 * v4 + 1], ph[4 * v4 + 2], ph[4 * v4 + 3]);
-        dl[v4] = make_uint4(pl[4 * v4], pl[4 * v4 + 1], pl[4 * v4 + 2], pl[4 * v4 + 3]);
+        const int piece = (4 * colhalf + v4) ^ (i & 7);
+        ih[piece] = make_uint4(ph[4 * v4], ph[4 * v4 + 1], ph[4 * v4 + 2], ph[4 * v4 + 3]);
+        il[piece] = make_uint4(pl[4 * v4], pl[4 * v4 + 1], pl[4 * v4 + 2], pl[4 * v4 + 3]);
       }
+      tc::fence_proxy_async_smem();
     }
   }
   __syncthreads();
+  if (tid == 0 && ok) {
+    tc::bulk_store(out.p_hi + rec * (C * C), smem + PP_PHI, REC_P);
+    tc::bulk_store(out.p_lo + rec * (C * C), smem + PP_PLO, REC_P);
+    tc::bulk_commit();
+  }
   PTRACE(5);
   // ---- T = (I + A)^-1 by 16x16 blocks.  With D = blockdiag(I + A_rr) and E = D^-1 (A - A_D) (strictly block lower,
   // E^4 = 0):  T = (I - E + E^2 - E^3) D^-1.  Only the four small D_r^-1 need a sequential substitution.
@@ -376,6 +387,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     const int j = tid - 64;
     fwv[j] = betas[j] * __expf(bs[j]) * kn[j];
   }
+  if (tid == 0) tc::bulk_wait_read<0>();  // the P images have been read: the block scratch may overwrite them
   __syncthreads();
   PTRACE(6);
   // E_rc = D_r^-1 A_rc, r > c: six products, one warp each
@@ -434,32 +446,48 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   __syncthreads();
   PTRACE(7);
   // Tw = T diag(beta e^b kn) as bf16 hi + lo K-major tiles [i][j] with the 128-byte swizzle (B operand of the W MMA);
-  // Tu = T diag(beta) as bf16 hi + lo rows straight to scratch (a warp writes one full 128-byte row per store)
+  // Tu = T diag(beta) as bf16 hi + lo rows straight to scratch.  A thread owns one 16-byte piece (8 columns) of two rows;
+  // a warp covers four full rows per store.
   {
-    const int j = (tid & 31) * 2;  // this thread's column pair; rows (tid >> 5) + 8 q
-    const float fu0 = betas[j], fu1 = betas[j + 1], fw0 = fwv[j], fw1 = fwv[j + 1];
-    const int cb = j >> 4;
-    uint32_t* guh = reinterpret_cast<uint32_t*>(out.tu_hi + rec * (C * C)) + (tid & 31);
-    uint32_t* gul = reinterpret_cast<uint32_t*>(out.tu_lo + rec * (C * C)) + (tid & 31);
+    const int pc = tid & 7, cb = pc >> 1;
+    float fw[8], fu[8];
+    {
+      const float4 a0 = *reinterpret_cast<const float4*>(fwv + 8 * pc), a1 = *reinterpret_cast<const float4*>(fwv + 8 * pc + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(betas + 8 * pc), b1 = *reinterpret_cast<const float4*>(betas + 8 * pc + 4);
+      fw[0] = a0.x; fw[1] = a0.y; fw[2] = a0.z; fw[3] = a0.w; fw[4] = a1.x; fw[5] = a1.y; fw[6] = a1.z; fw[7] = a1.w;
+      fu[0] = b0.x; fu[1] = b0.y; fu[2] = b0.z; fu[3] = b0.w; fu[4] = b1.x; fu[5] = b1.y; fu[6] = b1.z; fu[7] = b1.w;
+    }
+    uint4* guh = reinterpret_cast<uint4*>(out.tu_hi + rec * (C * C));
+    uint4* gul = reinterpret_cast<uint4*>(out.tu_lo + rec * (C * C));
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const int i = (tid >> 5) + 8 * q;
-      float t0 = 0.f, t1 = 0.f;
-      if (j <= i) {
-        const int rb = i >> 4;
-        const float* src = (rb == cb) ? Di + rb * BLK_FLOATS : Ab + tri(rb, cb) * BLK_FLOATS;
-        const float2 tv = *reinterpret_cast<const float2*>(src + (i & 15) * BLK_LD + (j & 15));
-        t0 = tv.x; t1 = (j + 1 <= i) ? tv.y : 0.f;
+    for (int it = 0; it < 2; ++it) {
+      const int i = (tid >> 3) + 32 * it, rb = i >> 4;
+      float t[8];
+      if (cb <= rb) {
+        const float* src = ((rb == cb) ? Di + rb * BLK_FLOATS : Ab + tri(rb, cb) * BLK_FLOATS) + (i & 15) * BLK_LD + (pc & 1) * 8;
+        const float4 t0 = *reinterpret_cast<const float4*>(src), t1 = *reinterpret_cast<const float4*>(src + 4);
+        t[0] = t0.x; t[1] = t0.y; t[2] = t0.z; t[3] = t0.w; t[4] = t1.x; t[5] = t1.y; t[6] = t1.z; t[7] = t1.w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t[e] = (8 * pc + e <= i) ? t[e] : 0.f;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t[e] = 0.f;
       }
-      const uint32_t off = (uint32_t)(i * 128 + ((((j >> 3) ^ (i & 7))) << 4) + (j & 7) * 2);
-      const float w0 = t0 * fw0, w1 = t1 * fw1, u0 = t0 * fu0, u1 = t1 * fu1;
-      const uint32_t wh = pack_bf16x2(w0, w1), uh = pack_bf16x2(u0, u1);
-      *reinterpret_cast<uint32_t*>(smem + PP_TWH + off) = wh;
-      *reinterpret_cast<uint32_t*>(smem + PP_TWL + off) =
-          pack_bf16x2(w0 - __uint_as_float(wh << 16), w1 - __uint_as_float(wh & 0xffff0000u));
+      uint32_t wh[4], wl[4], uh[4], ul[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float w0 = t[2 * w] * fw[2 * w], w1 = t[2 * w + 1] * fw[2 * w + 1];
+        const float u0 = t[2 * w] * fu[2 * w], u1 = t[2 * w + 1] * fu[2 * w + 1];
+        wh[w] = pack_bf16x2(w0, w1); uh[w] = pack_bf16x2(u0, u1);
+        wl[w] = pack_bf16x2(w0 - __uint_as_float(wh[w] << 16), w1 - __uint_as_float(wh[w] & 0xffff0000u));
+        ul[w] = pack_bf16x2(u0 - __uint_as_float(uh[w] << 16), u1 - __uint_as_float(uh[w] & 0xffff0000u));
+      }
+      const uint32_t off = (uint32_t)(i * 128 + ((pc ^ (i & 7)) << 4));
+      *reinterpret_cast<uint4*>(smem + PP_TWH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+      *reinterpret_cast<uint4*>(smem + PP_TWL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
       if (ok) {
-        guh[i * (C / 2)] = uh;
-        gul[i * (C / 2)] = pack_bf16x2(u0 - __uint_as_float(uh << 16), u1 - __uint_as_float(uh & 0xffff0000u));
+        guh[i * 8 + pc] = make_uint4(uh[0], uh[1], uh[2], uh[3]);
+        gul[i * 8 + pc] = make_uint4(ul[0], ul[1], ul[2], ul[3]);
       }
     }
   }
@@ -591,6 +619,7 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
+                     const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
                      const float* __restrict__ scal_ws, float* __restrict__ o_f32,
                      float* __restrict__ carry, int seg_c0, int seg_n) {
   extern __shared__ uint8_t smem_raw[];
@@ -693,8 +722,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tma_load_4d(st + ST_Q + 8192, &maps.q, &full[s], 64, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_K, &maps.k, &full[s], 0, hk, tok, sp.b);
         tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
-        tc::tma_load_2d(st + ST_PHI, &maps.p_hi, &full[s], 0, row);
-        tc::tma_load_2d(st + ST_PLO, &maps.p_lo, &full[s], 0, row);
+        tc::bulk_load(st + ST_PHI, p_hi_ws + rec * (C * C), REC_P, &full[s]);
+        tc::bulk_load(st + ST_PLO, p_lo_ws + rec * (C * C), REC_P, &full[s]);
         tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
         // V and Tu of chunk c replace those of chunk c-1 once the U^T MMAs of chunk c-1 have read them
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
@@ -1100,8 +1129,6 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     int rc;
     if ((rc = make_tmap(&maps.tu_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_tmap(&maps.tu_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    if ((rc = make_tmap(&maps.p_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    if ((rc = make_tmap(&maps.p_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.p_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     const uint32_t box4[4] = {64, 1, 64, 1};
     const uint64_t dq[4] = {D, (uint64_t)a.Hk, (uint64_t)a.T, (uint64_t)a.B};
     const uint64_t sq[4] = {2, (uint64_t)a.q_stride_h * 2, (uint64_t)a.q_stride_t * 2, (uint64_t)(a.B > 1 ? a.q_stride_b : a.q_stride_t * a.T) * 2};
@@ -1134,7 +1161,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.scal, o_f32, carry, 0, big);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, 0, big);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
     // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1153,7 +1180,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.scal, o_f32, carry, c0, cn);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, c0, cn);
       AVE_CUDA_TRY(cudaGetLastError());
       if (norm_per_range) {
         AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
