@@ -157,6 +157,37 @@ __device__ __forceinline__ void block_store(float* __restrict__ dst, const float
   }
 }
 
+// bf16 hi + lo images of a pair of fp32 values: hi = round-to-bf16, lo = bf16(x - hi); packed math on the pair
+__device__ __forceinline__ void split_pair(float2 x, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16x2(x.x, x.y);
+  const float2 h = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
+  const float2 l = __ffma2_rn(h, make_float2(-1.f, -1.f), x);
+  lo = pack_bf16x2(l.x, l.y);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Four gated Gram entries f_i kn_j e^{b_i - b_j} acc_j for columns j0..j0+3 (packed fp32 pairs); entry e is kept when
+// keep > e, where the caller passes keep = i - j0 for a strictly lower mask and i - j0 + 1 for a lower one.  The
+// difference b_i - b_j is formed before the scaling by log2(e), so nearby tokens lose no accuracy to large |b|.
+__device__ __forceinline__ void gate4(float (&out)[4], const uint32_t* acc, float bi, float fi, const float* bs_j, const float* kn_j,
+                                      int keep) {
+  const float4 b4 = *reinterpret_cast<const float4*>(bs_j), k4 = *reinterpret_cast<const float4*>(kn_j);
+  const float2 m1 = make_float2(-1.f, -1.f), bi2 = make_float2(bi, bi), fi2 = make_float2(fi, fi);
+  const float2 l2e = make_float2(1.4426950408889634f, 1.4426950408889634f);
+  const float2 x0 = __fmul2_rn(__ffma2_rn(make_float2(b4.x, b4.y), m1, bi2), l2e);
+  const float2 x1 = __fmul2_rn(__ffma2_rn(make_float2(b4.z, b4.w), m1, bi2), l2e);
+  const float2 e0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y)), e1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+  const float2 r0 = __fmul2_rn(__fmul2_rn(fi2, make_float2(__uint_as_float(acc[0]), __uint_as_float(acc[1]))),
+                               __fmul2_rn(make_float2(k4.x, k4.y), e0));
+  const float2 r1 = __fmul2_rn(__fmul2_rn(fi2, make_float2(__uint_as_float(acc[2]), __uint_as_float(acc[3]))),
+                               __fmul2_rn(make_float2(k4.z, k4.w), e1));
+  out[0] = keep > 0 ? r0.x : 0.f; out[1] = keep > 1 ? r0.y : 0.f;
+  out[2] = keep > 2 ? r1.x : 0.f; out[3] = keep > 3 ? r1.y : 0.f;
+}
+
 constexpr int PREP_THREADS = 256;
 // Regions are reused as their contents die, which keeps a CTA at 52 KB so that four fit on an SM:
 //   PP_KQ  [K_h0 | Q_h0 | K_h1 | Q_h1]   once the Gram MMA is done the Q halves hold the store images of P hi / P lo, then
@@ -258,9 +289,12 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
 
   PTRACE(1);
-  bool ok = tc::mbar_wait(tma_bar, 0, abort_flag);
-  PTRACE(2);
+  // Only warp 0 polls an mbarrier; the other warps park at the next CTA barrier (a hardware barrier costs no issue
+  // slots, a polling loop does) and learn of a failed wait through the abort flag.
+  bool ok = true;
   if (warp == 0) {
+    ok = tc::mbar_wait(tma_bar, 0, abort_flag);
+    PTRACE(2);
     tc::tc_fence_after_sync();
     const bool leader = tc::elect_one();
     if (ok && leader) {
@@ -277,6 +311,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   // row norms of k and q (the swizzle only permutes 16-byte pieces inside a 128-byte row, so a row sum needs no decode)
   if (a.flags & AVE_GDN_FLAG_QK_L2NORM) {
+    __syncthreads();  // warp 0 has seen the tiles land
     const int i = tid >> 2, part = tid & 3;
     float sk = 0.f, sq = 0.f;
 #pragma unroll
@@ -308,42 +343,51 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     sc[2 * C + tid] = __expf(bC);
   }
   PTRACE(3);
-  ok = ok && tc::mbar_wait(mma_bar, 0, abort_flag);
+  if (warp == 0) tc::mbar_wait(mma_bar, 0, abort_flag);
+  __syncthreads();
+  ok = *abort_flag == 0u;
   PTRACE(4);
   tc::tc_fence_after_sync();
   {
     const int quarter = warp & 3, colhalf = warp >> 2;
     const int r = quarter * 32 + lane;
+    // warps whose 32 columns all lie above their 32 rows (rows 0..31 against columns 32..63) have nothing to gate
+    const bool above = colhalf > (quarter & 1);
     uint32_t acc[32];
-    tc::tmem_ld32(tm + PT_GRAM + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
-    tc::tmem_ld_wait();
-    if (r < C) {  // A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j)
+    if (!above) {
+      tc::tmem_ld32(tm + PT_GRAM + ((uint32_t)(quarter * 32) << 16) + 32 * colhalf, acc);
+      tc::tmem_ld_wait();
+    }
+    if (r < C) {  // A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j); blocks above the diagonal are not stored
       const int i = r;
       const float bi = bs[i], fi = betas[i] * kn[i];
+      if (!above) {
 #pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
-        float av[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = 32 * colhalf + 4 * j4 + e;
-          av[e] = (i > j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[4 * j4 + e]) : 0.f;
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const int j0 = 32 * colhalf + 4 * j4;
+          float av[4];
+          gate4(av, acc + 4 * j4, bi, fi, bs + j0, kn + j0, i - j0);
+          if ((j0 >> 4) <= (i >> 4))
+            *reinterpret_cast<float4*>(Ab + tri(i >> 4, j0 >> 4) * BLK_FLOATS + (i & 15) * BLK_LD + (j0 & 15)) =
+                make_float4(av[0], av[1], av[2], av[3]);
         }
-        const int jb = (32 * colhalf + 4 * j4) >> 4;  // column block; blocks above the diagonal are not stored
-        if (jb <= (i >> 4))
-          *reinterpret_cast<float4*>(Ab + tri(i >> 4, jb) * BLK_FLOATS + (i & 15) * BLK_LD + ((32 * colhalf + 4 * j4) & 15)) =
-              make_float4(av[0], av[1], av[2], av[3]);
       }
     } else {      // P = lower_incl(e^{b_i-b_j} q_i.k_j), bf16 hi + lo
       const int i = r - C;
       const float bi = bs[i], fi = (i < cr.len) ? qn[i] * a.scale : 0.f;
       uint32_t ph[16], pl[16];
+      if (!above) {
 #pragma unroll
-      for (int w = 0; w < 16; ++w) {
-        const int j = 32 * colhalf + 2 * w;
-        const float p0 = (i >= j) ? fi * kn[j] * __expf(bi - bs[j]) * __uint_as_float(acc[2 * w]) : 0.f;
-        const float p1 = (i >= j + 1) ? fi * kn[j + 1] * __expf(bi - bs[j + 1]) * __uint_as_float(acc[2 * w + 1]) : 0.f;
-        ph[w] = pack_bf16x2(p0, p1);
-        pl[w] = pack_bf16x2(p0 - __uint_as_float(ph[w] << 16), p1 - __uint_as_float(ph[w] & 0xffff0000u));
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const int j0 = 32 * colhalf + 4 * j4;
+          float pv[4];
+          gate4(pv, acc + 4 * j4, bi, fi, bs + j0, kn + j0, i - j0 + 1);
+          split_pair(make_float2(pv[0], pv[1]), ph[2 * j4], pl[2 * j4]);
+          split_pair(make_float2(pv[2], pv[3]), ph[2 * j4 + 1], pl[2 * j4 + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int w = 0; w < 16; ++w) { ph[w] = 0u; pl[w] = 0u; }
       }
       // the Q halves are dead (the Gram MMA is complete): they take the swizzled tile images of P hi and P lo, which
       // leave with one bulk copy each
@@ -476,11 +520,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       uint32_t wh[4], wl[4], uh[4], ul[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const float w0 = t[2 * w] * fw[2 * w], w1 = t[2 * w + 1] * fw[2 * w + 1];
-        const float u0 = t[2 * w] * fu[2 * w], u1 = t[2 * w + 1] * fu[2 * w + 1];
-        wh[w] = pack_bf16x2(w0, w1); uh[w] = pack_bf16x2(u0, u1);
-        wl[w] = pack_bf16x2(w0 - __uint_as_float(wh[w] << 16), w1 - __uint_as_float(wh[w] & 0xffff0000u));
-        ul[w] = pack_bf16x2(u0 - __uint_as_float(uh[w] << 16), u1 - __uint_as_float(uh[w] & 0xffff0000u));
+        const float2 tp = make_float2(t[2 * w], t[2 * w + 1]);
+        split_pair(__fmul2_rn(tp, make_float2(fw[2 * w], fw[2 * w + 1])), wh[w], wl[w]);
+        split_pair(__fmul2_rn(tp, make_float2(fu[2 * w], fu[2 * w + 1])), uh[w], ul[w]);
       }
       const uint32_t off = (uint32_t)(i * 128 + ((pc ^ (i & 7)) << 4));
       *reinterpret_cast<uint4*>(smem + PP_TWH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
@@ -511,7 +553,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     __syncwarp();
   }
   PTRACE(8);
-  ok = ok && tc::mbar_wait(mma2_bar, 0, abort_flag);
+  if (warp == 0) tc::mbar_wait(mma2_bar, 0, abort_flag);
+  __syncthreads();
+  ok = ok && *abort_flag == 0u;
   PTRACE(9);
   tc::tc_fence_after_sync();
   {
@@ -529,11 +573,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     for (int p4 = 0; p4 < 4; ++p4) {
       uint32_t hi[4], lo[4];
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float v0 = __uint_as_float(acc[8 * p4 + 2 * w]), v1 = __uint_as_float(acc[8 * p4 + 2 * w + 1]);
-        hi[w] = pack_bf16x2(v0, v1);
-        lo[w] = pack_bf16x2(v0 - __uint_as_float(hi[w] << 16), v1 - __uint_as_float(hi[w] & 0xffff0000u));
-      }
+      for (int w = 0; w < 4; ++w)
+        split_pair(make_float2(__uint_as_float(acc[8 * p4 + 2 * w]), __uint_as_float(acc[8 * p4 + 2 * w + 1])), hi[w], lo[w]);
       const int piece = (4 * colhalf + p4) ^ (r & 7);
       ih[piece] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       il[piece] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -586,13 +627,6 @@ constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO 
                    TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
 
 
-// bf16 hi + lo images of a pair of fp32 values: hi = round-to-bf16, lo = bf16(x - hi); packed math on the pair
-__device__ __forceinline__ void split_pair(float2 x, uint32_t& hi, uint32_t& lo) {
-  hi = pack_bf16x2(x.x, x.y);
-  const float2 h = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
-  const float2 l = __ffma2_rn(h, make_float2(-1.f, -1.f), x);
-  lo = pack_bf16x2(l.x, l.y);
-}
 // Barrier among a group of warps built on an mbarrier so that, unlike bar.sync, the wait is bounded.
 __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
   __syncwarp();
