@@ -76,6 +76,24 @@ __global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, in
     for (int i = 0; i < cnt && run + i < max_chunks; ++i) chunk_seq[run + i] = n;
     run += cnt;
   }
+  // Launch order of the scan's CTAs: longest sequences first, so that the last CTAs to start are short ones and the
+  // SMs finish together (one CTA walks one sequence's chain).  Exact ranking up to 1024 sequences; beyond that the
+  // tail is short against the total anyway and the order is the input order.
+  int32_t* order = chunk_seq + max_chunks;
+  __syncthreads();
+  if (n_seqs <= 1024) {
+    const int me = threadIdx.x;
+    const int mine = me < n_seqs ? max(0, (cu_seqlens[me + 1] - cu_seqlens[me] + C - 1) / C) : -1;
+    part[me] = mine;
+    __syncthreads();
+    if (me < n_seqs) {
+      int rank = 0;
+      for (int m = 0; m < n_seqs; ++m) rank += (part[m] > mine || (part[m] == mine && m < me)) ? 1 : 0;
+      order[rank] = me;
+    }
+  } else {
+    for (int n = lo; n < hi; ++n) order[n] = n;
+  }
 }
 
 #ifdef AVE_TRACE
@@ -655,7 +673,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
                      const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
                      const float* __restrict__ scal_ws, float* __restrict__ o_f32,
-                     float* __restrict__ carry, int seg_c0, int seg_n) {
+                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, int seg_c0, int seg_n) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
@@ -675,7 +693,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x / a.Hv, h = blockIdx.x % a.Hv;
+  const int h = blockIdx.x % a.Hv;
+  const int n = seq_order ? seq_order[blockIdx.x / a.Hv] : blockIdx.x / a.Hv;  // varlen: longest sequences first
   const int hk = h / (a.Hv / a.Hk);
   SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
   if (seg_c0 > 0 && sp.ok && sp.len > 0 && seg_c0 * C >= sp.len) return;  // finished in an earlier launch
@@ -1043,7 +1062,7 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   const size_t recs = (size_t)L.chunks * a.Hv;
   auto up = [](size_t x) { return (x + 1023) & ~(size_t)1023; };
   size_t off = 0;
-  L.chunk_start = off; off = up(off + ((size_t)a.n_seqs + 1 + (size_t)L.chunks) * 4);  // prefix table + chunk -> sequence map
+  L.chunk_start = off; off = up(off + (2 * (size_t)a.n_seqs + 1 + (size_t)L.chunks) * 4);  // prefix table, chunk -> sequence map, scan order
   L.w_hi = off; off = up(off + recs * REC_W);
   L.w_lo = off; off = up(off + recs * REC_W);
   L.p_hi = off; off = up(off + recs * REC_P);
@@ -1187,6 +1206,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
   }
   float* o_f32 = a.z ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
   float* carry = reinterpret_cast<float*>(ws + L.carry);
+  const int32_t* seq_order = a.cu_seqlens ? chunk_start + a.n_seqs + 1 + L.chunks : nullptr;
   const dim3 prep_grid((unsigned)L.chunks, (unsigned)a.Hv);
   const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)a.Hv;
   SideStream* side = (L.segments > 1 && allow_side_stream) ? side_stream(dev) : nullptr;
@@ -1195,7 +1215,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, 0, big);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, 0, big);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
     // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1214,7 +1234,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, c0, cn);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, c0, cn);
       AVE_CUDA_TRY(cudaGetLastError());
       if (norm_per_range) {
         AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
