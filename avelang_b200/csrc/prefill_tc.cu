@@ -264,7 +264,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   const ChunkRef cr = find_chunk(a, chunk_start, c);
   if (!cr.ok || cr.cis < seg_c0 || cr.cis >= seg_c0 + seg_n) return;  // not in this launch's range of chunks
-  TL_START(compact_grid ? (seg_c0 + seg_n - 1) / seg_n : 0);
+  TL_START(compact_grid ? compact_grid - 1 : 0);
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
@@ -311,7 +311,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   // slots, a polling loop does) and learn of a failed wait through the abort flag.
   bool ok = true;
   if (warp == 0) {
-    ok = tc::mbar_wait(tma_bar, 0, abort_flag);
+    ok = tc::mbar_wait_warp(tma_bar, 0, abort_flag);
     PTRACE(2);
     tc::tc_fence_after_sync();
     const bool leader = tc::elect_one();
@@ -361,7 +361,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     sc[2 * C + tid] = __expf(bC);
   }
   PTRACE(3);
-  if (warp == 0) tc::mbar_wait(mma_bar, 0, abort_flag);
+  if (warp == 0) tc::mbar_wait_warp(mma_bar, 0, abort_flag);
   __syncthreads();
   ok = *abort_flag == 0u;
   PTRACE(4);
@@ -571,7 +571,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     __syncwarp();
   }
   PTRACE(8);
-  if (warp == 0) tc::mbar_wait(mma2_bar, 0, abort_flag);
+  if (warp == 0) tc::mbar_wait_warp(mma2_bar, 0, abort_flag);
   __syncthreads();
   ok = ok && *abort_flag == 0u;
   PTRACE(9);
@@ -615,7 +615,7 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
   PTRACE(10);
-  TL_END(compact_grid ? (seg_c0 + seg_n - 1) / seg_n : 0);
+  TL_END(compact_grid ? compact_grid - 1 : 0);
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
@@ -629,14 +629,16 @@ constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA is
 #endif
 constexpr int REGS_CTRL = AVE_REGS_CTRL, REGS_CHAIN = AVE_REGS_CHAIN, REGS_OUT = AVE_REGS_OUT;
 static_assert(REGS_CTRL + 2 * REGS_CHAIN + REGS_OUT <= 4 * 128, "register redistribution exceeds the launch allocation");
-constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728;
-constexpr int STAGE = 81920;                         // multiple of 1024
+constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728, ST_V = 81920;
+constexpr int STAGE = 98304;                         // multiple of 1024
 constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
 constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
 constexpr int OFF_SCAL = 2 * STAGE;                  // 4 x [qs | ks | decay]: a deeper ring than the tile stages, because
                                                      // the output warps read qs up to a chunk after the stage is recycled
-constexpr int OFF_VT = OFF_SCAL + 4 * SCAL_BYTES;    // single buffer: V tile (two 64-feature halves) | Tu hi | Tu lo
-constexpr int VT_V = 0, VT_TUH = 16384, VT_TUL = 24576, VT_BYTES = 32768;
+constexpr int OFF_VT = OFF_SCAL + 4 * SCAL_BYTES;    // single buffer: Tu hi | Tu lo (they come from scratch that pass 1 has
+                                                     // just written; the V tile, an input read with a long-latency strided
+                                                     // pattern, rides in the stage ring a chunk ahead)
+constexpr int VT_TUH = 0, VT_TUL = 8192, VT_BYTES = 16384;
 static_assert(OFF_VT % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 constexpr int OFF_BARS = OFF_VT + VT_BYTES;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
@@ -649,7 +651,7 @@ constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO 
 __device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
   __syncwarp();
   if (lane == 0) tc::mbar_arrive(bar);
-  const bool ok = tc::mbar_wait(bar, phase, abort_flag);
+  const bool ok = tc::mbar_wait_warp(bar, phase, abort_flag);
   phase ^= 1u;
   return ok;
 }
@@ -673,7 +675,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
                      const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
                      const float* __restrict__ scal_ws, float* __restrict__ o_f32,
-                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, int seg_c0, int seg_n) {
+                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, int seg_c0, int seg_n, int seg_idx) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
@@ -685,7 +687,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   uint64_t* dh_full = bars + 7;   // state increment accumulated
   uint64_t* o_full = bars + 8;    // both output accumulators complete
   uint64_t* o_empty = bars + 9;   // output accumulators drained
-  uint64_t* u_full = bars + 10;   // V and Tu tiles landed
+  uint64_t* u_full = bars + 10;   // Tu tiles landed
   uint64_t* u_empty = bars + 11;  // the U^T MMAs that read them are complete
   uint64_t* chain_bar = bars + 12;
   uint64_t* vd_ready = bars + 14; // Vd hi+lo written to TMEM (the state update needs nothing else)
@@ -753,7 +755,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  TL_START(8 + (seg_n < (1 << 20) ? (seg_c0 + seg_n - 1) / seg_n : 0));
+  (void)seg_idx;
+  TL_START(8 + seg_idx);
 
   if (warp < 4) {
   tc::reg_set<REGS_CTRL, 128>();
@@ -764,6 +767,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         const int s = c & 1;
         const uint32_t u = (uint32_t)(c >> 1);
         if (!tc::mbar_wait(&empty[s], (u & 1u) ^ 1u, abort_flag)) break;
+        TRACE(12, c);
         uint8_t* st = smem + s * STAGE;
         const int64_t rec = (int64_t)(c_first + c) * a.Hv + h;
         const int row = (int)(rec * C);
@@ -777,15 +781,16 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
         tc::bulk_load(st + ST_PHI, p_hi_ws + rec * (C * C), REC_P, &full[s]);
         tc::bulk_load(st + ST_PLO, p_lo_ws + rec * (C * C), REC_P, &full[s]);
+        tc::tma_load_4d(st + ST_V, &maps.v, &full[s], 0, h, tok, sp.b);
+        tc::tma_load_4d(st + ST_V + 8192, &maps.v, &full[s], 64, h, tok, sp.b);
         tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
-        // V and Tu of chunk c replace those of chunk c-1 once the U^T MMAs of chunk c-1 have read them
+        // Tu of chunk c replaces that of chunk c-1 once the U^T MMAs of chunk c-1 have read it
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
         uint8_t* vt = smem + OFF_VT;
         tc::mbar_expect_tx(u_full, VT_BYTES);
-        tc::tma_load_4d(vt + VT_V, &maps.v, u_full, 0, h, tok, sp.b);
-        tc::tma_load_4d(vt + VT_V + 8192, &maps.v, u_full, 64, h, tok, sp.b);
         tc::tma_load_2d(vt + VT_TUH, &maps.tu_hi, u_full, 0, row);
         tc::tma_load_2d(vt + VT_TUL, &maps.tu_lo, u_full, 0, row);
+        TRACE(15, c);
       }
     }
   } else if (warp == 1) {
@@ -796,28 +801,35 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
     constexpr uint32_t id_u = tc::idesc_f16(128, 64, 1, 1, true, false);                  // A = V tile read MN-major
     const uint32_t vtb = tc::smem_u32(smem + OFF_VT);
-    for (int c = 0; c < n_chunks; ++c) {
-      const int s = c & 1;
-      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-      const uint32_t sb = tc::smem_u32(smem + s * STAGE);
-      if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) break;
-      TRACE(0, c);
-      // U^T = V^T (Tu_hi + Tu_lo)^T opens the Vn^T accumulator; it does not depend on the state, so it runs while the
-      // chain epilogue is still re-packing H.  The previous chunk's O2 MMAs, which read these columns, were issued earlier
-      // by this thread and complete first.
-      if (!tc::mbar_wait(u_full, cp, abort_flag)) break;
+    // U^T = V^T (Tu_hi + Tu_lo)^T opens the Vn^T accumulator of a chunk.  It does not depend on the state, so it is
+    // issued a chunk ahead, right behind the previous chunk's O2 MMAs (which read the same columns and, issued earlier
+    // by this thread, complete first): the tensor pipe runs it while the chain epilogue re-packs H.
+    auto issue_u = [&](int c) -> bool {
+      const uint32_t vb = tc::smem_u32(smem + (c & 1) * STAGE + ST_V);
+      if (!tc::mbar_wait_warp(&full[c & 1], (uint32_t)(c >> 1) & 1u, abort_flag)) return false;  // the V tile rides in the stage
+      if (!tc::mbar_wait_warp(u_full, (uint32_t)c & 1u, abort_flag)) return false;
+      TRACE(13, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
 #pragma unroll
         for (int t = 0; t < 2; ++t)
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 16 tokens per step: V rows 2048 bytes apart, feature halves 8192 bytes apart
-            tc::mma_ss(tm + TM_VN, tc::smem_desc_sw128(vtb + VT_V + k * 2048, 8192, 1024),
+            tc::mma_ss(tm + TM_VN, tc::smem_desc_sw128(vb + k * 2048, 8192, 1024),
                        tc::smem_desc_sw128(vtb + (t ? VT_TUL : VT_TUH) + k * 32, 16, 1024), id_u, (t | k) != 0 ? 1u : 0u);
         tc::mma_commit(u_empty);
       }
       __syncwarp();
-      if (!tc::mbar_wait(h_ready, cp, abort_flag)) break;
+      TRACE(14, c);
+      return true;
+    };
+    bool issuing = n_chunks > 0 && issue_u(0);
+    for (int c = 0; c < n_chunks && issuing; ++c) {
+      const int s = c & 1;
+      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
+      const uint32_t sb = tc::smem_u32(smem + s * STAGE);  // the stage has landed: issue_u(c) waited for it
+      TRACE(0, c);
+      if (!tc::mbar_wait_warp(h_ready, cp, abort_flag)) break;
       TRACE(1, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
@@ -829,7 +841,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       }
       __syncwarp();
       TRACE(2, c);
-      if (!tc::mbar_wait(o_empty, cp ^ 1u, abort_flag)) break;
+      if (!tc::mbar_wait_warp(o_empty, cp ^ 1u, abort_flag)) break;
       TRACE(3, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
@@ -838,7 +850,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         issue_ts(tm + TM_O1, tm + TM_HLO, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, true);
       }
       __syncwarp();
-      if (!tc::mbar_wait(vd_ready, cp, abort_flag)) break;
+      if (!tc::mbar_wait_warp(vd_ready, cp, abort_flag)) break;
       TRACE(4, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
@@ -848,7 +860,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::mma_commit(dh_full);
       }
       __syncwarp();
-      if (!tc::mbar_wait(vn_ready, cp, abort_flag)) break;
+      if (!tc::mbar_wait_warp(vn_ready, cp, abort_flag)) break;
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // O2 = Vn_hi Phi^T + Vn_lo Phi^T + Vn_hi Plo^T
@@ -860,6 +872,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       }
       __syncwarp();
       TRACE(5, c);
+      if (c + 1 < n_chunks) issuing = issue_u(c + 1);
     }
   }
   } else if (warp < 12) {
@@ -904,9 +917,9 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
-      if (!tc::mbar_wait(&full[s], u & 1u, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait_warp(&full[s], u & 1u, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(6, c);
-      if (!tc::mbar_wait(vn_full, cp, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait_warp(vn_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(7, c);
       tc::tc_fence_after_sync();
       {
@@ -945,7 +958,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         }
       }
       if (warp == 4 && lane == 0) TRACE(8, c);
-      if (!tc::mbar_wait(dh_full, cp, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait_warp(dh_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 4 && lane == 0) TRACE(9, c);
       tc::tc_fence_after_sync();
       {
@@ -989,7 +1002,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const int64_t tok0 = sp.t0 + c * C;
       // o_full is committed by the MMA warp after it saw this chunk's stage (tiles and scale vectors) land, so it also
       // orders the scale vectors; waiting on the stage barrier here would alias phases once this warp lags a chunk
-      if (!tc::mbar_wait(o_full, cp, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait_warp(o_full, cp, abort_flag)) { alive = false; break; }
       if (warp == 12 && lane == 0) TRACE(11, c);
       tc::tc_fence_after_sync();
       float* pf = of ? of + tok0 * ((int64_t)a.Hv * D) : nullptr;
@@ -1035,7 +1048,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           }
         }
       }
-      if (warp == 12 && lane == 0) TRACE(12, c);
     }
   }
 
@@ -1046,9 +1058,14 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 512);
   }
-  TL_END(8 + (seg_n < (1 << 20) ? (seg_c0 + seg_n - 1) / seg_n : 0));
+  TL_END(8 + seg_idx);
 }
 
+#ifndef AVE_SEG_FIRST_DIV
+#define AVE_SEG_FIRST_DIV 16   // first range = 1/16 of the longest sequence's chunks
+#define AVE_SEG_GROWTH_X4 12   // each range 3x the one before (in quarters)
+#define AVE_SEG_MAX 8
+#endif
 struct WsLayout {
   size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, carry, total;
   int64_t chunks;
@@ -1075,15 +1092,22 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   // Few long chains (fewer scan CTAs than half the SMs): cut the sequences into ranges so that pass 1 of range i+1 runs
   // on the idle SMs while pass 2 of range i walks its chain.  The state crosses ranges through the carry buffer.
   const int max_chunks = (a.T + C - 1) / C;
-  L.segments = ((int64_t)a.n_seqs * a.Hv <= 74 && max_chunks >= 32) ? 5 : 1;
   L.seg_begin[0] = 0;
-  if (L.segments == 1) {
+  if (!((int64_t)a.n_seqs * a.Hv <= 74 && max_chunks >= 32)) {
+    L.segments = 1;
     L.seg_begin[1] = 1 << 24;  // every chunk (times 64 still fits an int)
   } else {
-    // a short first range (its pass 1 is the only one nothing overlaps), then four equal ones
-    const int first = (max_chunks + 15) / 16, rest = (max_chunks - first + 3) / 4;
-    L.seg_begin[1] = first;
-    for (int i = 2; i <= 5; ++i) L.seg_begin[i] = first + (i - 1) * rest;
+    // A short first range (its pass 1 is the only one nothing overlaps), then ranges that grow geometrically: pass 1
+    // of a range must fit inside pass 2 of the range before it, and per chunk pass 1 (on the idle SMs) is about twice
+    // as fast as the chain.
+    int len = max(1, (max_chunks + AVE_SEG_FIRST_DIV - 1) / AVE_SEG_FIRST_DIV);
+    L.segments = 0;
+    while (L.seg_begin[L.segments] < max_chunks) {
+      int next = L.seg_begin[L.segments] + len;
+      if (L.segments == AVE_SEG_MAX - 1 || next >= max_chunks) next = max_chunks;
+      L.seg_begin[++L.segments] = next;
+      len = max(len + 1, len * AVE_SEG_GROWTH_X4 / 4);
+    }
   }
   L.carry = off;
   if (L.segments > 1) off = up(off + (size_t)a.n_seqs * a.Hv * D * D * 4);
@@ -1215,7 +1239,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, 0, big);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
     // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1230,11 +1254,11 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
       const int c0 = L.seg_begin[i], cn = L.seg_begin[i + 1] - L.seg_begin[i];
       if (cn <= 0) continue;
       chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * cn), (unsigned)a.Hv), PREP_THREADS, smem_prep, side->prep>>>(
-          a, maps, chunk_start, po, c0, cn, 1);
+          a, maps, chunk_start, po, c0, cn, 1 + i);
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, c0, cn);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, c0, cn, i);
       AVE_CUDA_TRY(cudaGetLastError());
       if (norm_per_range) {
         AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
