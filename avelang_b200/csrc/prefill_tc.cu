@@ -112,7 +112,7 @@ __device__ long long g_trace[16 * 1024];
 #endif
 
 struct GdnMaps {
-  CUtensorMap q, k, v, tu_hi, tu_lo;
+  CUtensorMap q, k, v;
 };
 
 // ------------------------------------------------------------------------------------------------ pass 1
@@ -508,8 +508,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   __syncthreads();
   PTRACE(7);
   // Tw = T diag(beta e^b kn) as bf16 hi + lo K-major tiles [i][j] with the 128-byte swizzle (B operand of the W MMA);
-  // Tu = T diag(beta) as bf16 hi + lo rows straight to scratch.  A thread owns one 16-byte piece (8 columns) of two rows;
-  // a warp covers four full rows per store.
+  // Tu = T diag(beta) as bf16 hi + lo straight to scratch, in the same swizzled tile layout (the scan brings it in with
+  // a bulk copy).  A thread owns one 16-byte piece (8 columns) of two rows; a warp covers four full rows per store.
   {
     const int pc = tid & 7, cb = pc >> 1;
     float fw[8], fu[8];
@@ -546,8 +546,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       *reinterpret_cast<uint4*>(smem + PP_TWH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
       *reinterpret_cast<uint4*>(smem + PP_TWL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
       if (ok) {
-        guh[i * 8 + pc] = make_uint4(uh[0], uh[1], uh[2], uh[3]);
-        gul[i * 8 + pc] = make_uint4(ul[0], ul[1], ul[2], ul[3]);
+        guh[i * 8 + (pc ^ (i & 7))] = make_uint4(uh[0], uh[1], uh[2], uh[3]);  // same swizzled image as in shared memory
+        gul[i * 8 + (pc ^ (i & 7))] = make_uint4(ul[0], ul[1], ul[2], ul[3]);
       }
     }
   }
@@ -674,6 +674,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
                      const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
+                     const __nv_bfloat16* __restrict__ tu_hi_ws, const __nv_bfloat16* __restrict__ tu_lo_ws,
                      const float* __restrict__ scal_ws, float* __restrict__ o_f32,
                      float* __restrict__ carry, const int32_t* __restrict__ seq_order, int seg_c0, int seg_n, int seg_idx) {
   extern __shared__ uint8_t smem_raw[];
@@ -770,7 +771,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         TRACE(12, c);
         uint8_t* st = smem + s * STAGE;
         const int64_t rec = (int64_t)(c_first + c) * a.Hv + h;
-        const int row = (int)(rec * C);
         const int tok = sp.t0 + c * C;
         tc::mbar_expect_tx(&full[s], STAGE_TX);
         tc::bulk_load(st + ST_WHI, w_hi_ws + rec * (C * D), REC_W, &full[s]);  // W^T tile images: 128 d_k rows of 64 tokens
@@ -788,8 +788,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
         uint8_t* vt = smem + OFF_VT;
         tc::mbar_expect_tx(u_full, VT_BYTES);
-        tc::tma_load_2d(vt + VT_TUH, &maps.tu_hi, u_full, 0, row);
-        tc::tma_load_2d(vt + VT_TUL, &maps.tu_lo, u_full, 0, row);
+        tc::bulk_load(vt + VT_TUH, tu_hi_ws + rec * (C * C), REC_P, u_full);
+        tc::bulk_load(vt + VT_TUL, tu_lo_ws + rec * (C * C), REC_P, u_full);
         TRACE(15, c);
       }
     }
@@ -1199,13 +1199,8 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
   po.scal = reinterpret_cast<float*>(ws + L.scal);
 
   GdnMaps maps;
-  const uint64_t rows = (uint64_t)L.chunks * a.Hv * C;
   {
-    const uint64_t dp[2] = {C, rows}, spp[2] = {2, C * 2};
-    const uint32_t box[2] = {64, 64};
     int rc;
-    if ((rc = make_tmap(&maps.tu_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_hi, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    if ((rc = make_tmap(&maps.tu_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, po.tu_lo, 2, dp, spp, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     const uint32_t box4[4] = {64, 1, 64, 1};
     const uint64_t dq[4] = {D, (uint64_t)a.Hk, (uint64_t)a.T, (uint64_t)a.B};
     const uint64_t sq[4] = {2, (uint64_t)a.q_stride_h * 2, (uint64_t)a.q_stride_t * 2, (uint64_t)(a.B > 1 ? a.q_stride_b : a.q_stride_t * a.T) * 2};
@@ -1239,7 +1234,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
     chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, 0, big, 0);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, carry, seq_order, 0, big, 0);
     AVE_CUDA_TRY(cudaGetLastError());
   } else {
     // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1258,7 +1253,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.scal, o_f32, carry, seq_order, c0, cn, i);
+      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, carry, seq_order, c0, cn, i);
       AVE_CUDA_TRY(cudaGetLastError());
       if (norm_per_range) {
         AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));

@@ -46,13 +46,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-// Warp-collective form of the bounded wait: lane 0 polls and the outcome is broadcast.  A CTA with a dozen waiting
-// warps otherwise keeps 32 pollers per warp on the same shared-memory word, and every hand-off pays for that queue.
-// Must be called by all 32 lanes of a converged warp.
+// Bounded wait called by all 32 lanes of a converged warp.  Every lane polls: letting lane 0 poll alone and
+// broadcasting the outcome was measured and doubled the time of the scan (0.90 ms against 0.46 ms on an 8192-token
+// sequence), so the hand-off latency is not a matter of the number of pollers.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  uint32_t ok = 1u;
-  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 // One lane of a converged warp; the enclosing control flow stays warp-uniform, which lets the compiler keep
