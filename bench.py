@@ -407,7 +407,7 @@ def main():
             "config": workload_config(world),
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": 15 * args.steps,  # five chunk ranges x (prep, scan, gated norm)
+            "gpu_launches": 12 * args.steps,  # four chunk ranges (8, 24, 72, 24 chunks) x (prep, scan, gated norm)
             "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
