@@ -59,3 +59,40 @@ def test_fused_gather_matches_nccl_two_ranks(built_lib):
     ret = mgr.dict()
     mp.spawn(_rank_main, args=(2, port, ret), nprocs=2, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def _rank_tp(rank, world, port, ret):
+    """Row-parallel output projection on two ranks against the unsharded block on rank 0's GPU."""
+    import torch.distributed as dist
+    from avelang_b200.block import GdnBlockShard, GdnBlockTP
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        hidden, Hk, Hv, d, B, T = 256, 2, 4, 128, 1, 130
+        g = torch.Generator().manual_seed(0)
+        w_in = (0.02 * torch.randn(2 * Hk * d + 2 * Hv * d + 2 * Hv, hidden, generator=g)).bfloat16()
+        conv_w = (torch.randn(2 * Hk * d + Hv * d, 4, generator=g) / 2).bfloat16()
+        A_log, dt_bias = torch.rand(Hv, generator=g) * 2.77, 0.1 * torch.randn(Hv, generator=g)
+        w_out = (0.05 * torch.randn(hidden, Hv * d, generator=g)).bfloat16()
+        x = torch.randn(B, T, hidden, generator=g).bfloat16().cuda()
+        y = GdnBlockTP(w_in, conv_w, A_log, dt_bias, torch.ones(d), w_out, Hk=Hk, Hv=Hv, dk=d, dv=d, rank=rank, world=world,
+                       device=f"cuda:{rank}").forward(x)
+        heads = GdnBlockShard(w_in, conv_w, A_log, dt_bias, torch.ones(d), Hk=Hk, Hv=Hv, dk=d, dv=d, device=f"cuda:{rank}").forward(x)
+        ref = heads.reshape(B * T, -1).float() @ w_out.cuda().float().T
+        err = ((y.reshape(B * T, -1).float() - ref).norm() / ref.norm()).item()
+        ret[rank] = err
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_row_parallel_output_projection_two_ranks(built_lib):
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_tp, args=(2, port, ret), nprocs=2, join=True)
+    assert set(ret.keys()) == {0, 1} and all(e < 1e-2 for e in ret.values()), dict(ret)
