@@ -59,3 +59,22 @@ def test_block_with_output_projection_matches_unsharded(built_lib, checker):
         p = gemm.gemm_pipeline_transposed_b(o.reshape(B * T, -1), blk.w_out).float()
         acc = p if acc is None else acc + p
     assert O.rel_l2(acc.cpu(), ref.cpu()) < 1e-2
+
+
+def test_block_config4_full_size_prefix_and_shard(built_lib, checker):
+    """The block at its full configuration (B=4, T=32768, hidden 2048, 16 key / 32 value heads): every stage is causal,
+    so the first tokens of a batch row depend on nothing else and can be held against the CPU checker; and one of
+    eight head shards, run alone, reproduces its slice of the unsharded output."""
+    O, _ = checker
+    from avelang_b200.block import GdnBlockShard
+    hidden, Hk, Hv, d, B, T, P = 2048, 16, 32, 128, 4, 32768, 160
+    w_in, conv_w, A_log, dt_bias, norm_w = _params(hidden, Hk, Hv, d, seed=11)
+    x = torch.randn(B, T, hidden, generator=torch.Generator().manual_seed(12)).bfloat16()
+    xg = x.cuda()
+    y = GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d).forward(xg)
+    assert y.shape == (B, T, Hv, d) and bool(torch.isfinite(y.float()).all())
+    ref = O.gdn_block_ref(x[2:3, :P], w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d)
+    err = O.rel_l2(y[2:3, :P].float().cpu(), ref.bfloat16().float())
+    assert err < 5e-3, err
+    part = GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d, rank=5, world=8).forward_local(xg)
+    assert O.rel_l2(part.float().cpu(), y[:, :, 20:24].float().cpu()) < 1e-6

@@ -176,3 +176,25 @@ def test_prefill_config3_varlen_sample(gdn, checker):
                                    inp.initial_state[n:n + 1])
         check_o(O, o[:, a:b], o_ref)
         check_s(O, s[n:n + 1], s_ref)
+
+
+def test_prefill_config3_full_size(gdn, checker):
+    """The 256K-token packed varlen configuration at full size (64 sequences of 128..16384 tokens, nonzero initial
+    states): the shortest, the median and the longest sequence against the C checker, every state finite, and a
+    second run bit-identical (the scan walks the sequences longest first; the order must not leak into results)."""
+    O, C = checker
+    inp = synth.config3()
+    o, s = _run(gdn, inp)
+    o2, s2 = _run(gdn, inp)
+    assert torch.equal(o, o2) and torch.equal(s, s2)
+    assert bool(torch.isfinite(s).all()) and bool(torch.isfinite(o.float()).all())
+    cu = inp.cu_seqlens.tolist()
+    lens = inp.extras["lengths"]
+    assert sum(lens) == inp.q.shape[1] == cu[-1]
+    order = sorted(range(64), key=lambda n: lens[n])
+    for n in (order[0], order[32], order[-1]):
+        a, b = cu[n], cu[n + 1]
+        o_ref, s_ref = C.recurrent(inp.q[:, a:b], inp.k[:, a:b], inp.v[:, a:b], inp.g[:, a:b], inp.beta[:, a:b], inp.scale,
+                                   inp.initial_state[n:n + 1])
+        check_o(O, o[:, a:b], o_ref)
+        check_s(O, s[n:n + 1], s_ref)
