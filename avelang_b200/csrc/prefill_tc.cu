@@ -1,13 +1,14 @@
 // Chunked gated-delta-rule prefill on the tensor cores (d_k = d_v = 128, chunk 64).
 //
-// Pass 1, chunk_prep (one CTA per (chunk, value head), fully parallel, three CTAs per SM): in-chunk cumulative gate b,
+// Pass 1, chunk_prep (one CTA per (chunk, value head), fully parallel, four CTAs per SM): in-chunk cumulative gate b,
 //   [K; Q] K^T on tcgen05 -> A = strict_lower(beta_i e^{b_i-b_j} k_i.k_j) and P = scale * lower_incl(e^{b_i-b_j} q_i.k_j);
-//   T = (I+A)^-1 by 16x16 blocks (warp-level tf32 MMAs); W^T = K^T (T diag(beta e^b))^T and U^T = V^T (T diag(beta))^T on
-//   tcgen05.  W^T and P leave as bf16 hi+lo pairs (the tensor cores then see 16 significant bits), U^T as fp32, plus
-//   per-token scale vectors.
+//   T = (I+A)^-1 by 16x16 blocks (warp-level tf32 MMAs); W^T = K^T (T diag(beta e^b))^T on tcgen05.  W^T, P and
+//   Tu = T diag(beta) leave as bf16 hi+lo pairs (the tensor cores then see 16 significant bits), each as the swizzled
+//   shared-memory image of its tile so that a bulk copy moves it out here and in again in pass 2, plus per-token
+//   scale vectors.
 // Pass 2, chunk_scan (one CTA per (sequence, value head)): the recurrence over chunks with the state kept
 //   on chip, transposed (H = M^T, rows = d_v = TMEM lanes) so that every MMA has M = 128:
-//     Vn^T = U^T - H W^T                  (A = H hi/lo from TMEM, B = W^T hi/lo read MN-major)
+//     Vn^T = V^T Tu^T - H W^T             (A = V tile MN-major / H hi/lo from TMEM, B = Tu hi/lo, W^T hi/lo MN-major)
 //     O^T  = qs-scaled H Q^T + Vn^T P^T   (A = H or Vn hi/lo from TMEM, B = Q or P hi/lo, K-major)
 //     H   <- e^{b_C} H + Vd^T K           (A = Vd hi/lo from TMEM, B = K, MN-major), Vd_j = e^{b_C-b_j} Vn_j
 //   The fp32 master copy of H lives in the chain-epilogue threads' registers; its bf16 hi/lo image is rewritten to
@@ -229,7 +230,7 @@ constexpr uint32_t PT_GRAM = 0, PT_W = 0;               // TMEM columns (64 allo
 //   tensor cores: W^T = K^T (T diag(beta e^b))^T   (M = 128 = d_k, N = 64 tokens)
 // W^T leaves as bf16 hi + lo, as the 128-byte-swizzled shared-memory image of a [128][64] tile (one bulk copy out here,
 // one bulk copy in by the scan, which reads it as an MN-major B operand); Tu = T diag(beta) leaves as bf16 hi + lo
-// [64][64] row-major: the scan forms U^T = V^T Tu^T itself, straight into its Vn accumulator.
+// [64][64] tiles in the same swizzled layout: the scan forms U^T = V^T Tu^T itself, straight into its Vn accumulator.
 __global__ void __launch_bounds__(PREP_THREADS, 4)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out,
                   int seg_c0, int seg_n, int compact_grid) {
