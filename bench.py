@@ -411,7 +411,10 @@ def main():
             "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                        "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                        "frac": achieved / peaks["bf16_tflops"], "traffic": 471_699_248,
+                        "traffic_source": "profiles/prefill_config1_launch_list.md: DRAM bytes read + written by the four "
+                                          "chunk_scan launches of one step (the dominant kernel), ncu with its "
+                                          "cache flush between kernels; algorithmic bytes of the step are in hbm_view",
                         "peak_source": peaks["source"] + " (burst)",
                         "note": "algorithmic 42.95 GFLOP per step over the whole step (all launches): a lower bound "
                                 "for the dominant kernel",
