@@ -225,6 +225,36 @@ def fused_recurrent_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state
     return o, final
 
 
+def mixed_prefill_decode_step(q, k, v, g, beta, cu_seqlens, n_decode, state_pool, state_indices, scale=None,
+                              use_qk_l2norm_in_kernel=False, *, z=None, norm_weight=None, norm_eps=1e-6, out=None):
+    """One continuous-batching step over a packed batch (``B == 1``) ordered decode-first: sequences ``[0, n_decode)``
+    have exactly one token each and take the bandwidth-streaming decode kernel, the remaining sequences are prefill
+    (or chunked-prefill continuation) sequences of any length and take the chunked kernel.  Every sequence reads its
+    state from, and writes it back to, slot ``state_indices[n]`` of ``state_pool`` in place (a fresh sequence starts
+    from a zeroed slot).  ``cu_seqlens`` describes the whole packed batch; its first ``n_decode + 1`` entries must be
+    ``0, 1, ..., n_decode`` (not checked: that would need a device synchronisation).  Both launches go to the current
+    stream.  Returns ``o`` ``[1, T, Hv, dv]``."""
+    B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, z, cu_seqlens)
+    _req(cu_seqlens is not None and B == 1, "mixed_prefill_decode_step takes a packed batch: B == 1 with cu_seqlens")
+    _req(0 <= n_decode <= n_seqs and n_decode <= T, f"n_decode must lie in [0, {min(n_seqs, T)}], got {n_decode}.")
+    _req(state_pool is not None and state_indices is not None, "mixed_prefill_decode_step needs state_pool and state_indices")
+    o = _prep_out(out, v, z)
+    nd = int(n_decode)
+    if nd > 0:
+        step = lambda t: t[0, :nd].unsqueeze(1)  # [nd, 1, ...]: one single-token sequence per row
+        fused_recurrent_gated_delta_rule(step(q), step(k), step(v), step(g), step(beta), scale, initial_state=state_pool,
+                                         use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, state_indices=state_indices[:nd].contiguous(),
+                                         z=None if z is None else step(z), norm_weight=norm_weight, norm_eps=norm_eps, out=step(o))
+    if nd < n_seqs:
+        rest = lambda t: t[:, nd:]
+        chunk_gated_delta_rule(rest(q), rest(k), rest(v), rest(g), rest(beta), scale, initial_state=state_pool,
+                               output_final_state=True, use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
+                               cu_seqlens=(cu_seqlens[nd:] - nd).contiguous(), z=None if z is None else rest(z),
+                               norm_weight=norm_weight, norm_eps=norm_eps, state_indices=state_indices[nd:].contiguous(),
+                               out=rest(o))
+    return o
+
+
 def gated_rmsnorm(x, z, weight=None, eps=1e-6, *, gate_first=False, out=None):
     """``y = weight * x * rsqrt(mean(x^2) + eps) * silu(z)`` over the last dimension (64 or 128), bf16 in/out,
     fp32 math.  ``x``/``z``/``out``: ``[..., H, d]`` with a contiguous last dimension."""

@@ -198,3 +198,30 @@ def test_prefill_config3_full_size(gdn, checker):
                                    inp.initial_state[n:n + 1])
         check_o(O, o[:, a:b], o_ref)
         check_s(O, s[n:n + 1], s_ref)
+
+
+def test_mixed_prefill_decode_step(gdn, checker):
+    """A continuous-batching step: five single-token (decode) sequences followed by three prefill sequences in one
+    packed batch, all states in slots of one pool, fused gated norm.  Every sequence is held against the checker run
+    from its slot's state; slots no sequence uses stay untouched."""
+    O, C = checker
+    lens = [1, 1, 1, 1, 1, 70, 128, 33]
+    T, n_dec, n_slots = sum(lens), 5, 12
+    inp = synth.make_inputs(1, T, 2, 4, 128, 128, seed=21, with_z=True, n_states=n_slots, gate_scale=0.3)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    slots = torch.tensor([7, 2, 11, 0, 5, 9, 3, 6], dtype=torch.int32)
+    g = dev(inp)
+    pool = g.initial_state.clone()
+    o = gdn.mixed_prefill_decode_step(g.q, g.k, g.v, g.g, g.beta, cu.cuda(), n_dec, pool, slots.cuda(), z=g.z)
+    assert gdn.read_status() == 0
+    for n, L in enumerate(lens):
+        a, b = int(cu[n]), int(cu[n + 1])
+        sl = int(slots[n])
+        o_ref, s_ref = C.recurrent(inp.q[:, a:b], inp.k[:, a:b], inp.v[:, a:b], inp.g[:, a:b], inp.beta[:, a:b], inp.scale,
+                                   inp.initial_state[sl:sl + 1])
+        check_o(O, o[:, a:b], O.gated_rmsnorm(o_ref, inp.z[:, a:b]))
+        check_s(O, pool[sl:sl + 1], s_ref)
+    unused = [s for s in range(n_slots) if s not in slots.tolist()]
+    assert torch.equal(pool[unused].cpu(), inp.initial_state[unused])
+    with pytest.raises(ValueError):
+        gdn.mixed_prefill_decode_step(g.q, g.k, g.v, g.g, g.beta, cu.cuda(), 99, pool, slots.cuda())
