@@ -1101,13 +1101,17 @@ WsLayout ws_layout(const AveGdnArgs& a) {
     // A short first range (its pass 1 is the only one nothing overlaps), then ranges that grow geometrically: pass 1
     // of a range must fit inside pass 2 of the range before it, and per chunk pass 1 (on the idle SMs) is about twice
     // as fast as the chain.
-    int len = max(1, (max_chunks + AVE_SEG_FIRST_DIV - 1) / AVE_SEG_FIRST_DIV);
+    // With the fused all-gather the gated norm of a range also pushes that range's rows to every peer over NVLink,
+    // which takes about as long as the chain itself; only the last range's push is exposed, so the ranges are equal
+    // and as many as the event pool allows instead of growing.
+    const bool push = a.o_peers != nullptr && a.n_peers > 1;
+    int len = push ? (max_chunks + AVE_SEG_MAX - 1) / AVE_SEG_MAX : max(1, (max_chunks + AVE_SEG_FIRST_DIV - 1) / AVE_SEG_FIRST_DIV);
     L.segments = 0;
     while (L.seg_begin[L.segments] < max_chunks) {
       int next = L.seg_begin[L.segments] + len;
       if (L.segments == AVE_SEG_MAX - 1 || next >= max_chunks) next = max_chunks;
       L.seg_begin[++L.segments] = next;
-      len = max(len + 1, len * AVE_SEG_GROWTH_X4 / 4);
+      if (!push) len = max(len + 1, len * AVE_SEG_GROWTH_X4 / 4);
     }
   }
   L.carry = off;
