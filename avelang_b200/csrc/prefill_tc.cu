@@ -1122,8 +1122,8 @@ WsLayout ws_layout(const AveGdnArgs& a) {
 
 }  // namespace
 
-int launch_gated_rmsnorm_f32in(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers = nullptr, int n_peers = 0,
-                               int64_t peer_off = 0);
+int launch_gated_rmsnorm_f32in_batched(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers, int n_peers,
+                                       int64_t peer_off, int batches, int64_t xs_b, int64_t zs_b, int64_t ys_b);
 
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
 
@@ -1168,25 +1168,22 @@ static SideStream* side_stream(int dev) {
   return &s;
 }
 
-// Gated RMSNorm over the fp32 output for tokens [t_begin, t_end) of every batch row.
+// Gated RMSNorm over the fp32 output for tokens [t_begin, t_end) of every batch row, one launch.
 static int norm_rows(const AveGdnArgs& a, float* o_f32, int t_begin, int t_end, cudaStream_t stream) {
   if (t_end <= t_begin) return AVE_GDN_OK;
-  for (int b = 0; b < a.B; ++b) {
-    AveGdnNormArgs nb{};
-    nb.struct_size = sizeof(nb);
-    nb.flags = a.flags & AVE_GDN_FLAG_GATE_FIRST;
-    nb.rows = (int64_t)(t_end - t_begin) * a.Hv;
-    nb.d = D; nb.heads = a.Hv; nb.eps = a.norm_eps; nb.weight = a.norm_weight;
-    nb.x = o_f32 + ((int64_t)b * a.T + t_begin) * a.Hv * D;
-    nb.x_stride_t = (int64_t)a.Hv * D; nb.x_stride_h = D;
-    nb.z = reinterpret_cast<const __nv_bfloat16*>(a.z) + b * a.z_stride_b + (int64_t)t_begin * a.z_stride_t;
-    nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
-    nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t;
-    nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
-    const int rc = launch_gated_rmsnorm_f32in(nb, stream, a.o_peers, a.n_peers, (int64_t)b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t);
-    if (rc != AVE_GDN_OK) return rc;
-  }
-  return AVE_GDN_OK;
+  AveGdnNormArgs nb{};
+  nb.struct_size = sizeof(nb);
+  nb.flags = a.flags & AVE_GDN_FLAG_GATE_FIRST;
+  nb.rows = (int64_t)(t_end - t_begin) * a.Hv;
+  nb.d = D; nb.heads = a.Hv; nb.eps = a.norm_eps; nb.weight = a.norm_weight;
+  nb.x = o_f32 + (int64_t)t_begin * a.Hv * D;
+  nb.x_stride_t = (int64_t)a.Hv * D; nb.x_stride_h = D;
+  nb.z = reinterpret_cast<const __nv_bfloat16*>(a.z) + (int64_t)t_begin * a.z_stride_t;
+  nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
+  nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + (int64_t)t_begin * a.o_stride_t;
+  nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
+  return launch_gated_rmsnorm_f32in_batched(nb, stream, a.o_peers, a.n_peers, (int64_t)t_begin * a.o_stride_t, a.B,
+                                            (int64_t)a.T * a.Hv * D, a.z_stride_b, a.o_stride_b);
 }
 
 int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream) {
