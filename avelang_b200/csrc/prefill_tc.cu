@@ -1182,8 +1182,23 @@ static int norm_rows(const AveGdnArgs& a, float* o_f32, int t_begin, int t_end, 
   nb.z_stride_t = a.z_stride_t; nb.z_stride_h = a.z_stride_h;
   nb.y = reinterpret_cast<__nv_bfloat16*>(a.o) + (int64_t)t_begin * a.o_stride_t;
   nb.y_stride_t = a.o_stride_t; nb.y_stride_h = a.o_stride_h;
-  return launch_gated_rmsnorm_f32in_batched(nb, stream, a.o_peers, a.n_peers, (int64_t)t_begin * a.o_stride_t, a.B,
-                                            (int64_t)a.T * a.Hv * D, a.z_stride_b, a.o_stride_b);
+  // With peers the launch covers every batch row at once (many short launches keep too few peer stores in flight);
+  // without, one launch per batch row measured 1-2 % faster on four rows of a million norm rows each.
+  const bool push = a.o_peers != nullptr && a.n_peers > 1;
+  const int64_t xs_b = (int64_t)a.T * a.Hv * D;
+  if (push || a.B == 1)
+    return launch_gated_rmsnorm_f32in_batched(nb, stream, a.o_peers, a.n_peers, (int64_t)t_begin * a.o_stride_t, a.B, xs_b,
+                                              a.z_stride_b, a.o_stride_b);
+  for (int b = 0; b < a.B; ++b) {
+    AveGdnNormArgs one = nb;
+    one.x = reinterpret_cast<const float*>(nb.x) + b * xs_b;
+    one.z = reinterpret_cast<const __nv_bfloat16*>(nb.z) + b * a.z_stride_b;
+    one.y = reinterpret_cast<__nv_bfloat16*>(nb.y) + b * a.o_stride_b;
+    const int rc = launch_gated_rmsnorm_f32in_batched(one, stream, a.o_peers, a.n_peers,
+                                                      (int64_t)b * a.o_stride_b + (int64_t)t_begin * a.o_stride_t, 1, 0, 0, 0);
+    if (rc != AVE_GDN_OK) return rc;
+  }
+  return AVE_GDN_OK;
 }
 
 int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream) {
