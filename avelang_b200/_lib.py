@@ -22,7 +22,7 @@ class GdnArgs(ctypes.Structure):
                 + [(n, P) for n in ("q", "k", "v", "g", "beta", "z", "norm_weight", "o", "initial_state",
                                     "final_state", "cu_seqlens", "state_indices", "status", "workspace")]
                 + [("workspace_bytes", U64)]
-                + [(n, I32) for n in ("B", "T", "Hk", "Hv", "dk", "dv", "n_seqs", "num_slots", "chunk", "reserved0")]
+                + [(n, I32) for n in ("B", "T", "Hk", "Hv", "dk", "dv", "n_seqs", "num_slots", "chunk", "max_seqlen")]
                 + [(f"{t}_stride_{d}", I64) for t in ("q", "k", "v", "z", "o") for d in ("b", "t", "h")]
                 + [("g_stride_b", I64), ("g_stride_t", I64), ("scale", F32), ("norm_eps", F32),
                    ("o_peers", P), ("n_peers", I32), ("reserved1", I32)])

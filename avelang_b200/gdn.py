@@ -169,7 +169,8 @@ def _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, device, want_
 
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                            use_qk_l2norm_in_kernel=False, cu_seqlens=None, *, z=None, norm_weight=None,
-                           norm_eps=1e-6, state_indices=None, inplace_state=True, chunk_size=64, out=None, out_peers=None):
+                           norm_eps=1e-6, state_indices=None, inplace_state=True, chunk_size=64, out=None, out_peers=None,
+                           max_seqlen=None):
     """Chunked (chunk 64) gated delta rule over whole sequences.  Returns ``(o, final_state or None)``.
 
     With ``z`` the gated RMSNorm ``rmsnorm(o) * silu(z)`` (weight ``norm_weight``, eps ``norm_eps``) is fused and
@@ -179,9 +180,15 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     ``out_peers`` (needs ``z``): int64 device tensor of base addresses of buffers laid out exactly like ``out``, one per
     GPU of the node (peer-mapped, this GPU's included).  The normalised rows are then stored into all of them by the
     norm kernel itself (a fused all-gather over NVLink) instead of into ``out``; the caller must put a barrier between
-    this call and any reader of those buffers."""
+    this call and any reader of those buffers.
+
+    ``max_seqlen`` (with ``cu_seqlens``): an upper bound of the longest sequence, known to the host.  With it the chunk
+    ranges of the overlapped schedule (used for batches of few long sequences) are sized from the real chain length
+    instead of the packed total; results are the same with or without it.  A sequence longer than the bound is skipped and flagged in the status word, like a
+    malformed ``cu_seqlens`` entry."""
     B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, z, cu_seqlens)
     _req(chunk_size == 64, f"chunk_size must be 64, got {chunk_size}.")
+    _req(max_seqlen is None or int(max_seqlen) >= 0, f"max_seqlen must be non-negative, got {max_seqlen}.")
     o = _prep_out(out, v, z)
     norm_weight = _prep_norm_weight(norm_weight, z, dv, q.device)
     final, num_slots = _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, q.device,
@@ -189,6 +196,8 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
     a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
                    state_indices, num_slots, n_seqs, flags)
+    if max_seqlen is not None and cu_seqlens is not None:
+        a.max_seqlen = min(int(max_seqlen), T)
     if out_peers is not None:
         _req(z is not None, "out_peers needs z (the stores are fused into the gated norm)")
         _req(out_peers.dtype == torch.int64 and out_peers.dim() == 1 and out_peers.device == q.device and out_peers.is_contiguous(),

@@ -285,7 +285,9 @@ def bench_varlen(args, rank, world):
     s0, cu = inp.initial_state[:, vs].contiguous().cuda(), inp.cu_seqlens.cuda()
     out = torch.empty_like(v)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
-    step = lambda: gdn.chunk_gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=True, cu_seqlens=cu, out=out)
+    longest = max(inp.extras["lengths"])  # the host built the batch, so it knows the longest sequence
+    step = lambda: gdn.chunk_gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=True, cu_seqlens=cu, out=out,
+                                              max_seqlen=longest)
     with ClockSampler(torch.cuda.current_device()) as clocks:
         total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
     ms = total_ms / args.steps

@@ -79,7 +79,9 @@ typedef struct AveGdnArgs {
   int32_t n_seqs;    /* B when cu_seqlens is null */
   int32_t num_slots; /* tiles in the state arrays; n_seqs when state_indices is null */
   int32_t chunk;     /* prefill: 64 */
-  int32_t reserved0;
+  int32_t max_seqlen; /* optional, with cu_seqlens: an upper bound of the longest sequence in tokens (0 = unknown).  It
+                         sizes the launch schedule of the prefill; a sequence longer than it is skipped and flagged
+                         AVE_GDN_DEV_BAD_SEQLEN. */
   int64_t q_stride_b, q_stride_t, q_stride_h;
   int64_t k_stride_b, k_stride_t, k_stride_h;
   int64_t v_stride_b, v_stride_t, v_stride_h;

@@ -225,3 +225,24 @@ def test_mixed_prefill_decode_step(gdn, checker):
     assert torch.equal(pool[unused].cpu(), inp.initial_state[unused])
     with pytest.raises(ValueError):
         gdn.mixed_prefill_decode_step(g.q, g.k, g.v, g.g, g.beta, cu.cuda(), 99, pool, slots.cuda())
+
+
+def test_prefill_varlen_max_seqlen_hint(gdn, checker):
+    """With the longest sequence known, the chunk ranges of a packed batch of few long chains (16 sequences x 4 heads)
+    are sized from it; results are bit-identical to the schedule sized from the packed total, and a sequence longer
+    than the stated bound is skipped and flagged."""
+    O, C = checker
+    inp = synth.config3(n_seqs=16, total=32768, lo=128, hi=8192, Hk=2, Hv=4)
+    lens = inp.extras["lengths"]
+    o0, s0 = _run(gdn, inp)
+    o1, s1 = _run(gdn, inp, max_seqlen=max(lens))
+    assert gdn.read_status() == 0
+    assert torch.equal(o0, o1) and torch.equal(s0, s1)
+    n = max(range(16), key=lambda i: lens[i])
+    a, b = int(inp.cu_seqlens[n]), int(inp.cu_seqlens[n + 1])
+    o_ref, s_ref = C.recurrent(inp.q[:, a:b], inp.k[:, a:b], inp.v[:, a:b], inp.g[:, a:b], inp.beta[:, a:b], inp.scale,
+                               inp.initial_state[n:n + 1])
+    check_o(O, o1[:, a:b], o_ref)
+    check_s(O, s1[n:n + 1], s_ref)
+    _run(gdn, inp, max_seqlen=max(lens) - 1)
+    assert gdn.read_status() & 2  # AVE_GDN_DEV_BAD_SEQLEN
