@@ -233,6 +233,8 @@ def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0):
     from avelang_b200 import synth
     from oracle import c_oracle
     inp = synth.config1(T=sample_tokens)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = c_oracle.set_threads(cores) or 1  # all the cores this process may use, whatever OMP_NUM_THREADS the launcher set
     t = time.perf_counter()
     c_oracle.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, precision="f32")  # untimed warm-up
     if reps is None:
@@ -243,7 +245,7 @@ def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0):
         c_oracle.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, precision="f32")
         times.append(time.perf_counter() - t)
     sec = statistics.median(times)
-    return {"value": sample_tokens / sec, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+    return {"value": sample_tokens / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"full workload (T={sample_tokens}, 32 value heads, d=128), fp32 token recurrence in C with "
                       f"OpenMP, median of {reps} runs, {sec:.3f} s each"}
 

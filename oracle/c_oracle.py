@@ -26,6 +26,17 @@ def _lib():
     return _LIB
 
 
+def set_threads(n: int) -> int:
+    """Sets the OpenMP team size of the C routines (launchers such as torchrun export OMP_NUM_THREADS=1, which would
+    otherwise pin the timed CPU baseline to one core).  Returns the count set, 0 if the OpenMP runtime was not found."""
+    _lib()  # makes sure the runtime the library links against is loaded
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(n))
+        return int(n)
+    except OSError:
+        return 0
+
+
 def recurrent(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=None, precision="f64",
               use_qk_l2norm_in_kernel=False):
     """Same function as gdn_oracle.naive_recurrent_gated_delta_rule, run by the C checker.
