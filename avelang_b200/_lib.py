@@ -15,6 +15,7 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, MISALIGNED, CUDA_ERROR, WORKSPACE_TOO_SMALL =
 DEV_BAD_SLOT, DEV_BAD_SEQLEN, DEV_WAIT_EXPIRED = 1, 2, 4
 FLAG_QK_L2NORM, FLAG_GATE_FIRST = 1, 2
 NOALLOC_SCRATCH_BYTES = 64 << 20
+ABI_VERSION = 3
 
 
 class GdnArgs(ctypes.Structure):
@@ -37,7 +38,7 @@ class NormArgs(ctypes.Structure):
 
 class GemmArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("c", P),
-                ("M", I64), ("N", I64), ("K", I64), ("lda", I64), ("ldb", I64), ("ldc", I64)]
+                ("M", I64), ("N", I64), ("K", I64), ("lda", I64), ("ldb", I64), ("ldc", I64), ("status", P)]
 
 
 class ConvArgs(ctypes.Structure):
@@ -49,7 +50,7 @@ class ConvArgs(ctypes.Structure):
 class ConvUpdateArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("x", P), ("w", P), ("bias", P), ("y", P), ("conv_state", P),
                 ("state_indices", P), ("n_seqs", I32), ("C", I32), ("width", I32), ("num_slots", I32),
-                ("x_stride", I64), ("y_stride", I64)]
+                ("x_stride", I64), ("y_stride", I64), ("status", P)]
 
 
 class GateArgs(ctypes.Structure):
@@ -93,7 +94,7 @@ def load():
         for name, (res, args) in SYMBOLS.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
-        if lib.ave_gdn_abi_version() != 2:
+        if lib.ave_gdn_abi_version() != ABI_VERSION:
             raise ImportError("libave_gdn_b200.so has an unexpected ABI version")
         _LIB = lib
     return _LIB

@@ -16,7 +16,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libave_gdn_b200.so")
 SOURCES = ["api.cu", "decode.cu", "rmsnorm.cu", "prefill_simt.cu", "elementwise.cu", "gemm.cu", "tmap.cu", "prefill_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math" if False else "-DAVE_NO_FAST_MATH", "-Xcompiler", "-fPIC", "-I" + INCLUDE,
+              "-Xcompiler", "-fPIC", "-I" + INCLUDE,
               "-I" + CSRC]
 
 

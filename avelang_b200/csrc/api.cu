@@ -8,8 +8,8 @@ thread_local int g_last_cuda_error = 0;
 int launch_decode(const AveGdnArgs& a, cudaStream_t stream);
 int launch_prefill_simt(const AveGdnArgs& a, cudaStream_t stream);
 size_t prefill_simt_workspace_bytes(const AveGdnArgs& a);
-int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream = true);
-size_t prefill_tc_workspace_bytes(const AveGdnArgs& a);
+int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain);
+size_t prefill_tc_workspace_bytes(const AveGdnArgs& a, bool plain);
 int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream);
 int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
@@ -17,7 +17,7 @@ int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
 
 static size_t prefill_ws_bytes(const AveGdnArgs& a) {
-  return a.dk == 128 ? prefill_tc_workspace_bytes(a) : prefill_simt_workspace_bytes(a);
+  return a.dk == 128 ? prefill_tc_workspace_bytes(a, false) : prefill_simt_workspace_bytes(a);
 }
 
 static int check_rows(const void* p, int64_t st, int64_t sh, int64_t sb, int elem_bytes) {
@@ -87,7 +87,7 @@ int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream) {
   if (args->workspace == nullptr || !aligned16(args->workspace)) return AVE_GDN_INVALID_ARGUMENT;
   if (args->workspace_bytes < prefill_ws_bytes(*args)) return AVE_GDN_WORKSPACE_TOO_SMALL;
   // d = 128 runs on the tensor cores; d = 64 (the small CPU-reference shape) on the fp32 CUDA-core kernels
-  if (args->dk == 128) return launch_prefill_tc(*args, reinterpret_cast<cudaStream_t>(stream));
+  if (args->dk == 128) return launch_prefill_tc(*args, reinterpret_cast<cudaStream_t>(stream), false);
   return launch_prefill_simt(*args, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -120,7 +120,11 @@ __global__ void __launch_bounds__(128) conv1d_update_kernel(const AveConvUpdateA
   const int n = blockIdx.y;
   if (cg * 8 >= a.C) return;
   int slot = a.state_indices ? a.state_indices[n] : n;
-  if (slot < 0 || slot >= a.num_slots) return;
+  if (slot >= a.num_slots) {
+    if (a.status != nullptr && threadIdx.x == 0 && blockIdx.x == 0) atomicOr(a.status, AVE_GDN_DEV_BAD_SLOT);
+    return;
+  }
+  if (slot < 0) return;
   __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(a.conv_state) + (int64_t)slot * (WIDTH - 1) * a.C + cg * 8;
   auto unpack8 = [](uint4 raw, float (&f)[8]) {
     f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);

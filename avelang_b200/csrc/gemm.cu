@@ -172,7 +172,7 @@ int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream) {
   const int64_t tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
   gemm_bf16_nt_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(a.c), a.M, a.N, a.K,
-                                                               a.ldc, nullptr);
+                                                               a.ldc, a.status);
   AVE_CUDA_TRY(cudaGetLastError());
   return AVE_GDN_OK;
 }

@@ -36,20 +36,29 @@ struct ScratchRec {
 };
 
 // chunk_start[n] = number of chunks of sequences 0..n-1 (varlen only); one CTA of 1024 threads.
-__global__ void chunk_table_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int32_t* __restrict__ chunk_start) {
+// The scratch is sized for T/64 + n_seqs chunks, which holds exactly when the offsets are monotone inside [0, T]; a table
+// that breaks this is rejected as a whole: total = -1 (every CTA of the two passes tests it and leaves), status bit set.
+__global__ void chunk_table_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int T, int32_t* __restrict__ chunk_start,
+                                   uint32_t* __restrict__ status) {
   __shared__ int part[1024];
   const int per = (n_seqs + 1023) / 1024;
   const int lo = threadIdx.x * per, hi = min(lo + per, n_seqs);
-  int s = 0;
-  for (int n = lo; n < hi; ++n) s += max(0, (cu_seqlens[n + 1] - cu_seqlens[n] + kChunk - 1) / kChunk);
+  int s = 0, bad = 0;
+  for (int n = lo; n < hi; ++n) {
+    const int a0 = cu_seqlens[n], a1 = cu_seqlens[n + 1];
+    bad |= (a0 < 0 || a1 < a0 || a1 > T) ? 1 : 0;
+    s += max(0, (a1 - a0 + kChunk - 1) / kChunk);
+  }
   part[threadIdx.x] = s;
-  __syncthreads();
+  bad = __syncthreads_or(bad);
   if (threadIdx.x == 0) {
     int run = 0;
     for (int i = 0; i < 1024; ++i) { const int x = part[i]; part[i] = run; run += x; }
-    chunk_start[n_seqs] = run;
+    chunk_start[n_seqs] = bad ? -1 : run;
+    if (bad && status != nullptr) atomicOr(status, AVE_GDN_DEV_BAD_SEQLEN);
   }
   __syncthreads();
+  if (bad) return;
   int run = part[threadIdx.x];
   for (int n = lo; n < hi; ++n) {
     chunk_start[n] = run;
@@ -238,6 +247,7 @@ __global__ void __launch_bounds__(256) chunk_scan_kernel(const AveGdnArgs a, con
   const int n = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * NS;
   const int hk = h / (a.Hv / a.Hk);
   const int tid = threadIdx.x;
+  if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;  // the chunk table was rejected
   const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
   if (!sp.ok) return;
 
@@ -353,7 +363,7 @@ static int launch_prefill_t(const AveGdnArgs& a, cudaStream_t stream) {
   off += (size_t)chunks * a.Hv * R::kFloats * sizeof(float);
   float* o_f32 = a.z ? reinterpret_cast<float*>(ws + off) : nullptr;
 
-  if (a.cu_seqlens != nullptr) chunk_table_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start);
+  if (a.cu_seqlens != nullptr) chunk_table_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, a.T, chunk_start, a.status);
 
   constexpr size_t smem_local = sizeof(float) * (2 * kChunk * (DK + 1) + kChunk * (kChunk + 1) + 4 * kChunk);
   constexpr size_t smem_scan = sizeof(float) * (3 * kChunk * DK + kChunk * kChunk + DK * kDvSlice + 2 * kChunk * kDvSlice + kChunk);

@@ -17,6 +17,8 @@
 //   With a gate tensor z the un-normalised output goes to fp32 scratch and a gated-RMSNorm launch finishes it
 //   (optionally storing each row into every GPU's buffer: the fused all-gather).
 // All waits are bounded; on give-up the CTA drains, frees its tensor memory and sets a status bit.
+#include <mutex>
+
 #include "common.cuh"
 #include "tc.cuh"
 
@@ -54,21 +56,34 @@ __device__ __forceinline__ ChunkRef find_chunk(const AveGdnArgs& a, const int32_
   return r;
 }
 
-__global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int32_t* __restrict__ chunk_start,
-                                      int max_chunks) {
+// One CTA of 1024 threads builds the chunk tables of a packed batch: chunk_start[n] = chunks of sequences 0..n-1,
+// chunk_start[n_seqs] = their total, then the chunk -> sequence map and the scan's launch order.  The scratch behind the
+// tables is sized for T/64 + n_seqs chunks, which holds exactly when the offsets are monotone and stay inside [0, T];
+// a table that breaks this would send later sequences' records past their regions, so the whole batch is skipped
+// instead: the total is stored as -1 (every CTA of the following launches tests it and leaves) and the status word gets
+// AVE_GDN_DEV_BAD_SEQLEN.
+__global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int T, int32_t* __restrict__ chunk_start,
+                                      int max_chunks, uint32_t* __restrict__ status) {
   __shared__ int part[1024];
   const int per = (n_seqs + 1023) / 1024;
   const int lo = threadIdx.x * per, hi = min(lo + per, n_seqs);
-  int s = 0;
-  for (int n = lo; n < hi; ++n) s += max(0, (cu_seqlens[n + 1] - cu_seqlens[n] + C - 1) / C);
+  int s = 0, bad = 0;
+  for (int n = lo; n < hi; ++n) {
+    const int a0 = cu_seqlens[n], a1 = cu_seqlens[n + 1];
+    bad |= (a0 < 0 || a1 < a0 || a1 > T) ? 1 : 0;
+    s += max(0, (a1 - a0 + C - 1) / C);
+  }
   part[threadIdx.x] = s;
-  __syncthreads();
+  bad = __syncthreads_or(bad);
   if (threadIdx.x == 0) {
     int run = 0;
     for (int i = 0; i < 1024; ++i) { const int x = part[i]; part[i] = run; run += x; }
-    chunk_start[n_seqs] = run;
+    bad |= run > max_chunks ? 1 : 0;
+    chunk_start[n_seqs] = bad ? -1 : run;
+    if (bad && status != nullptr) atomicOr(status, AVE_GDN_DEV_BAD_SEQLEN);
   }
   __syncthreads();
+  if (bad) return;
   int run = part[threadIdx.x];
   int32_t* chunk_seq = chunk_start + n_seqs + 1;  // chunk_seq[c] = sequence that owns chunk c
   for (int n = lo; n < hi; ++n) {
@@ -97,24 +112,32 @@ __global__ void chunk_table_tc_kernel(const int32_t* __restrict__ cu_seqlens, in
   }
 }
 
-#ifdef AVE_TRACE
-__device__ unsigned long long g_tl[64];  // [slot][0] = earliest CTA start, [slot][1] = latest CTA end (globaltimer ns)
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TL_START(slot) do { if (threadIdx.x == 0) atomicMin(&g_tl[2 * (slot)], gtime()); } while (0)
-#define TL_END(slot) do { if (threadIdx.x == 0) atomicMax(&g_tl[2 * (slot) + 1], gtime()); } while (0)
-__device__ long long g_trace[16 * 1024];
-#define PTRACE(slot) do { if (blockIdx.x == 300 && blockIdx.y == 7 && threadIdx.x == 0) g_trace[16 * 1000 + (slot)] = clock64(); } while (0)
-#define TRACE(slot, c) do { if (blockIdx.x == 0 && (c) < 1024) g_trace[(c) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot, c) do {} while (0)
-#define TL_START(slot) do {} while (0)
-#define TL_END(slot) do {} while (0)
-#define PTRACE(slot) do {} while (0)
-#endif
 
 struct GdnMaps {
   CUtensorMap q, k, v;
 };
+
+// How one launch cuts the chunks of every sequence.
+//   parts : a sequence's chunks are cut into up to `parts` consecutive parts, [part_begin[p], part_begin[p+1]), that are
+//           scanned at the same time by different CTAs.  Part 0 starts from the true initial state.  A later part p runs
+//           two chains: a local one from a zero state (its outputs miss the contribution of the state M0(p) that enters
+//           the part) and a transition chain, the same recurrence with v = 0 started from the identity, whose state is
+//           the part's transition matrix F (M_end = F M0 + local end state) and whose "output" is qt_t = scale F_t^T q_t,
+//           so that the missing contribution is M0(p)^T qt_t: one GEMM per part once M0(p) is known.
+//   ranges: independently, a launch covers only the chunk offsets [r0, r0 + rn) inside every part, so that pass 1 of a
+//           later range runs while pass 2 walks an earlier one; a chain's state crosses launches in the carry buffer.
+constexpr int MAX_PARTS = 8;
+struct ScanPlan {
+  int parts;
+  int part_begin[MAX_PARTS + 1];  // part_begin[parts] = 1 << 24
+  int r0, rn;
+};
+__device__ __forceinline__ int part_of(const ScanPlan& pl, int cis) {
+  int p = 0;
+#pragma unroll
+  for (int i = 1; i < MAX_PARTS; ++i) p += (i < pl.parts && cis >= pl.part_begin[i]) ? 1 : 0;
+  return p;
+}
 
 // ------------------------------------------------------------------------------------------------ pass 1
 // Shared memory of chunk_prep (offsets from a 1024-byte aligned base).  The K and Q tiles are interleaved by
@@ -233,7 +256,7 @@ constexpr uint32_t PT_GRAM = 0, PT_W = 0;               // TMEM columns (64 allo
 // [64][64] tiles in the same swizzled layout: the scan forms U^T = V^T Tu^T itself, straight into its Vn accumulator.
 __global__ void __launch_bounds__(PREP_THREADS, 4)
 chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start, PrepOut out,
-                  int seg_c0, int seg_n, int compact_grid) {
+                  const __grid_constant__ ScanPlan plan, int compact_grid) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* Ab = reinterpret_cast<float*>(smem + PP_A);   // A as 16x16 blocks (r >= c), block tri(r,c); later T
@@ -254,22 +277,27 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 
   const int h = blockIdx.y, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  // Whole-batch launches index every chunk of the batch; range launches (seg_n chunks per sequence) use the compact
-  // grid n_seqs x seg_n so that no CTA is spent on chunks outside the range.
+  // Whole-batch launches index every chunk of the batch; range launches use the compact grid
+  // n_seqs x parts x rn so that no CTA is spent on chunks outside the range.
   int c = blockIdx.x;
   if (compact_grid) {
-    const int n = blockIdx.x / seg_n, cis = seg_c0 + blockIdx.x % seg_n;
+    const int per_seq = plan.parts * plan.rn;
+    const int n = blockIdx.x / per_seq, rest = blockIdx.x % per_seq;
+    const int cis = plan.part_begin[rest / plan.rn] + plan.r0 + rest % plan.rn;
+    if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;  // table rejected
     const int per = a.cu_seqlens ? (chunk_start[n + 1] - chunk_start[n]) : (a.T + C - 1) / C;
-    if (cis >= per) return;
+    if (cis >= per || cis >= plan.part_begin[rest / plan.rn + 1]) return;
     c = (a.cu_seqlens ? chunk_start[n] : n * per) + cis;
   }
   const ChunkRef cr = find_chunk(a, chunk_start, c);
-  if (!cr.ok || cr.cis < seg_c0 || cr.cis >= seg_c0 + seg_n) return;  // not in this launch's range of chunks
-  TL_START(compact_grid ? compact_grid - 1 : 0);
+  if (!cr.ok) return;
+  {
+    const int off = cr.cis - plan.part_begin[part_of(plan, cr.cis)];
+    if (off < plan.r0 || off >= plan.r0 + plan.rn) return;  // not in this launch's range of chunks
+  }
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
-  PTRACE(0);
   if (tid == 0) {
     tc::mbar_init(tma_bar, 1);
     tc::mbar_init(mma_bar, 1);
@@ -282,7 +310,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::tma_load_4d(smem + PP_KQ + 16384, &maps.k, tma_bar, 64, hk, cr.t0, cr.b);
     tc::tma_load_4d(smem + PP_KQ + 24576, &maps.q, tma_bar, 64, hk, cr.t0, cr.b);
   }
-  PTRACE(13);
   if (warp == 2) tc::tmem_alloc(tmem_slot, 64);
   if (tid < C) {
     const bool valid = tid < cr.len;
@@ -290,11 +317,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     bs[tid] = valid ? a.g[off] : 0.f;
     betas[tid] = valid ? a.beta[off] : 0.f;
   }
-  PTRACE(14);
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
-  PTRACE(15);
   const uint32_t tm = *tmem_slot;
   if (warp == 1) {  // in-chunk cumulative gate: inclusive scan of 64 values by one warp
     float v0 = bs[lane], v1 = bs[32 + lane];
@@ -307,13 +332,11 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     bs[lane] = v0; bs[32 + lane] = v1;
   }
 
-  PTRACE(1);
   // Only warp 0 polls an mbarrier; the other warps park at the next CTA barrier (a hardware barrier costs no issue
   // slots, a polling loop does) and learn of a failed wait through the abort flag.
   bool ok = true;
   if (warp == 0) {
     ok = tc::mbar_wait_warp(tma_bar, 0, abort_flag);
-    PTRACE(2);
     tc::tc_fence_after_sync();
     const bool leader = tc::elect_one();
     if (ok && leader) {
@@ -361,11 +384,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     sc[C + tid] = __expf(bC - bs[tid]) * kn[tid];    // Vd_j = ks_j Vn_j
     sc[2 * C + tid] = __expf(bC);
   }
-  PTRACE(3);
   if (warp == 0) tc::mbar_wait_warp(mma_bar, 0, abort_flag);
   __syncthreads();
   ok = *abort_flag == 0u;
-  PTRACE(4);
   tc::tc_fence_after_sync();
   {
     const int quarter = warp & 3, colhalf = warp >> 2;
@@ -427,7 +448,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::bulk_store(out.p_lo + rec * (C * C), smem + PP_PLO, REC_P);
     tc::bulk_commit();
   }
-  PTRACE(5);
   // ---- T = (I + A)^-1 by 16x16 blocks.  With D = blockdiag(I + A_rr) and E = D^-1 (A - A_D) (strictly block lower,
   // E^4 = 0):  T = (I - E + E^2 - E^3) D^-1.  Only the four small D_r^-1 need a sequential substitution.
   if (tid < 64) {  // column k of (I + A_rr)^-1, 16 rows, one thread each
@@ -452,7 +472,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
   }
   if (tid == 0) tc::bulk_wait_read<0>();  // the P images have been read: the block scratch may overwrite them
   __syncthreads();
-  PTRACE(6);
   // E_rc = D_r^-1 A_rc, r > c: six products, one warp each
   if (warp < 6) {
     constexpr int RR[6] = {1, 2, 2, 3, 3, 3}, CC[6] = {0, 0, 1, 0, 1, 2};
@@ -507,7 +526,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     block_store(Ab + tri(r, c) * BLK_FLOATS, acc, lane);
   }
   __syncthreads();
-  PTRACE(7);
   // Tw = T diag(beta e^b kn) as bf16 hi + lo K-major tiles [i][j] with the 128-byte swizzle (B operand of the W MMA);
   // Tu = T diag(beta) as bf16 hi + lo straight to scratch, in the same swizzled tile layout (the scan brings it in with
   // a bulk copy).  A thread owns one 16-byte piece (8 columns) of two rows; a warp covers four full rows per store.
@@ -571,11 +589,9 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     }
     __syncwarp();
   }
-  PTRACE(8);
   if (warp == 0) tc::mbar_wait_warp(mma2_bar, 0, abort_flag);
   __syncthreads();
   ok = ok && *abort_flag == 0u;
-  PTRACE(9);
   tc::tc_fence_after_sync();
   {
     // Each lane owns one row of W^T (a d_k index) and each warp half of its 64 tokens.  The K, Q and Tw tiles are dead
@@ -599,7 +615,6 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
       il[piece] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
   }
-  PTRACE(11);
   tc::fence_proxy_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -609,26 +624,18 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     tc::bulk_commit();
     tc::bulk_wait_read<0>();  // shared memory must stay intact until the copies have read it
   }
-  PTRACE(12);
   if (warp == 2) {
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 64);
   }
   if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
-  PTRACE(10);
-  TL_END(compact_grid ? compact_grid - 1 : 0);
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
 constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA issuer; warpgroups 1,2: chain epilogue (two
                                     // column groups); warpgroup 3: output.  Launch allocation is 128 registers per thread,
                                     // redistributed below as 72 / 176 / 176 / 88 (sum 512).
-#ifndef AVE_REGS_CTRL
-#define AVE_REGS_CTRL 72
-#define AVE_REGS_CHAIN 176
-#define AVE_REGS_OUT 88
-#endif
-constexpr int REGS_CTRL = AVE_REGS_CTRL, REGS_CHAIN = AVE_REGS_CHAIN, REGS_OUT = AVE_REGS_OUT;
+constexpr int REGS_CTRL = 72, REGS_CHAIN = 176, REGS_OUT = 88;
 static_assert(REGS_CTRL + 2 * REGS_CHAIN + REGS_OUT <= 4 * 128, "register redistribution exceeds the launch allocation");
 constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728, ST_V = 81920;
 constexpr int STAGE = 98304;                         // multiple of 1024
@@ -676,8 +683,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
                      const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
                      const __nv_bfloat16* __restrict__ tu_hi_ws, const __nv_bfloat16* __restrict__ tu_lo_ws,
-                     const float* __restrict__ scal_ws, float* __restrict__ o_f32,
-                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, int seg_c0, int seg_n, int seg_idx) {
+                     const float* __restrict__ scal_ws, float* __restrict__ o_f32, float* __restrict__ qt_f32,
+                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, const __grid_constant__ ScanPlan plan) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
@@ -697,9 +704,17 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // One CTA per (sequence, chain, value head).  Chain 0 is part 0; chains 2p-1 and 2p are the local and the transition
+  // chain of part p >= 1 (see ScanPlan).
+  const int chains = 2 * plan.parts - 1;
   const int h = blockIdx.x % a.Hv;
-  const int n = seq_order ? seq_order[blockIdx.x / a.Hv] : blockIdx.x / a.Hv;  // varlen: longest sequences first
+  const int unit = blockIdx.x / a.Hv;
+  const int chain = unit % chains;
+  const int n = seq_order ? seq_order[unit / chains] : unit / chains;  // varlen: longest sequences first
+  const int part = (chain + 1) >> 1;
+  const bool phi = chain > 0 && (chain & 1) == 0;
   const int hk = h / (a.Hv / a.Hk);
+  if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;  // the chunk table was rejected: nothing runs
   SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
   if (a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen) {
     // longer than the caller's bound: the launch schedule was sized from that bound, so the sequence is skipped and
@@ -707,9 +722,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     if (a.status != nullptr && threadIdx.x == 0) atomicOr(a.status, AVE_GDN_DEV_BAD_SEQLEN);
     sp.ok = false; sp.len = 0;
   }
-  if (seg_c0 > 0 && sp.ok && sp.len > 0 && seg_c0 * C >= sp.len) return;  // finished in an earlier launch
   if (!sp.ok || sp.len == 0) {
-    if (seg_c0 > 0) return;
+    if (plan.r0 > 0 || chain > 0) return;
     // zero-length sequence: the final state is the initial state
     if (sp.ok && a.final_state != nullptr && a.final_state != a.initial_state) {
       const int slot0 = a.state_indices ? a.state_indices[n] : n;
@@ -721,6 +735,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
     return;
   }
+  const int seq_chunks = (sp.len + C - 1) / C;
+  // a sequence that ends inside part 0 is one plain chain: outputs and the final state leave directly
+  const bool multi = plan.parts > 1 && seq_chunks > plan.part_begin[1];
+  if (chain > 0 && (!multi || plan.part_begin[part] >= seq_chunks)) return;
   int slot = n;
   if (a.state_indices != nullptr) {
     slot = a.state_indices[n];
@@ -730,23 +748,32 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
   }
   __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (int64_t)h * a.o_stride_h;
-  if (slot < 0) {
+  // where this chain's per-token rows go: the transition chain's qt rows and the local rows of later parts wait in fp32
+  // scratch for the fix-up; part 0 writes fp32 scratch only when a gated norm follows, else the result itself
+  float* const out_f32 = phi ? qt_f32 : ((a.z != nullptr || part > 0) ? o_f32 : nullptr);
+  if (slot < 0) {  // skipped sequence: zero output, no state access (chain 0 clears the whole sequence once)
+    if (chain > 0 || plan.r0 > 0) return;
+    float* zf = a.z != nullptr ? o_f32 : nullptr;
     for (int e = threadIdx.x; e < sp.len * D; e += SCAN_THREADS) {
       const int64_t tok = sp.t0 + e / D;
-      if (o_f32 != nullptr) o_f32[(((int64_t)sp.b * a.T + tok) * a.Hv + h) * D + e % D] = 0.f;
+      if (zf != nullptr) zf[(((int64_t)sp.b * a.T + tok) * a.Hv + h) * D + e % D] = 0.f;
       else og[tok * a.o_stride_t + e % D] = __float2bfloat16(0.f);
     }
     return;
   }
-  // A launch covers chunks [seg_c0, seg_c0 + seg_n) of every sequence: from here on the sequence is narrowed to that
-  // range, and the state enters from / leaves to the carry buffer unless this is the sequence's first / last range.
-  const bool seg_first = seg_c0 == 0;
-  const bool seg_last = (seg_c0 + seg_n) * C >= sp.len;
-  const int c_first = (a.cu_seqlens ? chunk_start[n] : n * ((a.T + C - 1) / C)) + seg_c0;
-  sp.t0 += seg_c0 * C;
-  sp.len = min(sp.len - seg_c0 * C, seg_n * C);
-  const int n_chunks = (sp.len + C - 1) / C;
-  const int64_t carry_tile = ((int64_t)n * a.Hv + h) * (int64_t)(D * D);
+  // This launch covers chunks [c_lo, c_hi) of the chain's part; the state enters from / leaves to the carry buffer
+  // unless this is the first / last launch of a plain chain.
+  const int part_end = min(plan.part_begin[part + 1], seq_chunks);
+  const int c_lo = plan.part_begin[part] + plan.r0;
+  const int c_hi = min(c_lo + plan.rn, part_end);
+  if (c_lo >= c_hi) return;  // finished in an earlier launch, or not reached yet
+  const bool seg_first = plan.r0 == 0;
+  const bool seg_last = c_hi == part_end && !multi;
+  const int c_first = (a.cu_seqlens ? chunk_start[n] : n * ((a.T + C - 1) / C)) + c_lo;
+  sp.t0 += c_lo * C;
+  sp.len = min(sp.len - c_lo * C, (c_hi - c_lo) * C);
+  const int n_chunks = c_hi - c_lo;
+  const int64_t carry_tile = (((int64_t)n * chains + chain) * a.Hv + h) * (int64_t)(D * D);
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&full[0], 1); tc::mbar_init(&full[1], 1);
@@ -763,8 +790,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  (void)seg_idx;
-  TL_START(8 + seg_idx);
 
   if (warp < 4) {
   tc::reg_set<REGS_CTRL, 128>();
@@ -775,11 +800,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         const int s = c & 1;
         const uint32_t u = (uint32_t)(c >> 1);
         if (!tc::mbar_wait(&empty[s], (u & 1u) ^ 1u, abort_flag)) break;
-        TRACE(12, c);
         uint8_t* st = smem + s * STAGE;
         const int64_t rec = (int64_t)(c_first + c) * a.Hv + h;
         const int tok = sp.t0 + c * C;
-        tc::mbar_expect_tx(&full[s], STAGE_TX);
+        tc::mbar_expect_tx(&full[s], phi ? STAGE_TX - 16384u : STAGE_TX);  // the transition chain has no V
         tc::bulk_load(st + ST_WHI, w_hi_ws + rec * (C * D), REC_W, &full[s]);  // W^T tile images: 128 d_k rows of 64 tokens
         tc::bulk_load(st + ST_WLO, w_lo_ws + rec * (C * D), REC_W, &full[s]);
         tc::tma_load_4d(st + ST_Q, &maps.q, &full[s], 0, hk, tok, sp.b);
@@ -788,16 +812,18 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
         tc::bulk_load(st + ST_PHI, p_hi_ws + rec * (C * C), REC_P, &full[s]);
         tc::bulk_load(st + ST_PLO, p_lo_ws + rec * (C * C), REC_P, &full[s]);
-        tc::tma_load_4d(st + ST_V, &maps.v, &full[s], 0, h, tok, sp.b);
-        tc::tma_load_4d(st + ST_V + 8192, &maps.v, &full[s], 64, h, tok, sp.b);
+        if (!phi) {
+          tc::tma_load_4d(st + ST_V, &maps.v, &full[s], 0, h, tok, sp.b);
+          tc::tma_load_4d(st + ST_V + 8192, &maps.v, &full[s], 64, h, tok, sp.b);
+        }
         tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
+        if (phi) continue;
         // Tu of chunk c replaces that of chunk c-1 once the U^T MMAs of chunk c-1 have read it
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
         uint8_t* vt = smem + OFF_VT;
         tc::mbar_expect_tx(u_full, VT_BYTES);
         tc::bulk_load(vt + VT_TUH, tu_hi_ws + rec * (C * C), REC_P, u_full);
         tc::bulk_load(vt + VT_TUL, tu_lo_ws + rec * (C * C), REC_P, u_full);
-        TRACE(15, c);
       }
     }
   } else if (warp == 1) {
@@ -814,8 +840,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     auto issue_u = [&](int c) -> bool {
       const uint32_t vb = tc::smem_u32(smem + (c & 1) * STAGE + ST_V);
       if (!tc::mbar_wait_warp(&full[c & 1], (uint32_t)(c >> 1) & 1u, abort_flag)) return false;  // the V tile rides in the stage
+      if (phi) return true;  // v = 0: U^T = 0, the first Vn MMA below overwrites the accumulator instead
       if (!tc::mbar_wait_warp(u_full, (uint32_t)c & 1u, abort_flag)) return false;
-      TRACE(13, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
 #pragma unroll
@@ -827,7 +853,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::mma_commit(u_empty);
       }
       __syncwarp();
-      TRACE(14, c);
       return true;
     };
     bool issuing = n_chunks > 0 && issue_u(0);
@@ -835,21 +860,17 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const uint32_t sb = tc::smem_u32(smem + s * STAGE);  // the stage has landed: issue_u(c) waited for it
-      TRACE(0, c);
       if (!tc::mbar_wait_warp(h_ready, cp, abort_flag)) break;
-      TRACE(1, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // Vn^T += -(Hhi Whi^T + Hhi Wlo^T + Hlo Whi^T); W^T is one [128 d_k][64 token] tile, 16 d_k rows per step
-        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
+        issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WHI, 2048, 0, 16, id_vn, 8, !phi);
         issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 2048, 0, 16, id_vn, 8, true);
         issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
         tc::mma_commit(vn_full);
       }
       __syncwarp();
-      TRACE(2, c);
       if (!tc::mbar_wait_warp(o_empty, cp ^ 1u, abort_flag)) break;
-      TRACE(3, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // O1 = (Hhi + Hlo) Q^T
@@ -858,7 +879,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       }
       __syncwarp();
       if (!tc::mbar_wait_warp(vd_ready, cp, abort_flag)) break;
-      TRACE(4, c);
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // dH = (Vd_hi + Vd_lo) contracted with K over the chunk's tokens (K tile read MN-major: 16 token rows per step)
@@ -878,7 +898,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::mma_commit(&empty[s]);
       }
       __syncwarp();
-      TRACE(5, c);
       if (c + 1 < n_chunks) issuing = issue_u(c + 1);
     }
   }
@@ -894,9 +913,15 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     uint32_t sync_phase = 0;
 
     float2 Hreg[32];  // H[d][64*grp + 2w .. +1] = M[64*grp + 2w .. +1][d]
-    const float* state_in = seg_first ? (a.initial_state ? a.initial_state + tile : nullptr) : carry + carry_tile;
+    // first launch of a chain: part 0 starts from the caller's state, a later part's local chain from zero and its
+    // transition chain from the identity
+    const float* state_in = !seg_first ? carry + carry_tile : (part == 0 && a.initial_state ? a.initial_state + tile : nullptr);
     float* state_out = seg_last ? (a.final_state ? a.final_state + tile : nullptr) : carry + carry_tile;
-    if (state_in != nullptr) {
+    if (phi && seg_first) {
+#pragma unroll
+      for (int w = 0; w < 32; ++w)
+        Hreg[w] = make_float2(64 * grp + 2 * w == d ? 1.f : 0.f, 64 * grp + 2 * w + 1 == d ? 1.f : 0.f);
+    } else if (state_in != nullptr) {
 #pragma unroll
       for (int w = 0; w < 32; ++w)
         Hreg[w] = make_float2(state_in[(int64_t)(64 * grp + 2 * w) * D + d], state_in[(int64_t)(64 * grp + 2 * w + 1) * D + d]);
@@ -925,9 +950,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
       if (!tc::mbar_wait_warp(&full[s], u & 1u, abort_flag)) { alive = false; break; }
-      if (warp == 4 && lane == 0) TRACE(6, c);
       if (!tc::mbar_wait_warp(vn_full, cp, abort_flag)) { alive = false; break; }
-      if (warp == 4 && lane == 0) TRACE(7, c);
       tc::tc_fence_after_sync();
       {
         uint32_t acc[32];
@@ -964,9 +987,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           if (lane == 0) tc::mbar_arrive(vn_ready);
         }
       }
-      if (warp == 4 && lane == 0) TRACE(8, c);
       if (!tc::mbar_wait_warp(dh_full, cp, abort_flag)) { alive = false; break; }
-      if (warp == 4 && lane == 0) TRACE(9, c);
       tc::tc_fence_after_sync();
       {
         const float decay = scal[2 * C];
@@ -983,7 +1004,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         publish_h();
       }
       if (lane == 0) tc::mbar_arrive(&empty[s]);  // this warp no longer reads the stage's scale vectors
-      if (warp == 4 && lane == 0) TRACE(10, c);
     }
     if (alive && state_out != nullptr) {
 #pragma unroll
@@ -1000,7 +1020,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     const int quarter = warp & 3;
     const int d = quarter * 32 + lane;
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
-    float* of = o_f32 ? o_f32 + ((int64_t)sp.b * a.T * a.Hv + h) * D + d : nullptr;
+    float* of = out_f32 ? out_f32 + ((int64_t)sp.b * a.T * a.Hv + h) * D + d : nullptr;
     bool alive = true;
     for (int c = 0; c < n_chunks && alive; ++c) {
       const uint32_t cp = (uint32_t)c & 1u;
@@ -1010,7 +1030,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       // o_full is committed by the MMA warp after it saw this chunk's stage (tiles and scale vectors) land, so it also
       // orders the scale vectors; waiting on the stage barrier here would alias phases once this warp lags a chunk
       if (!tc::mbar_wait_warp(o_full, cp, abort_flag)) { alive = false; break; }
-      if (warp == 12 && lane == 0) TRACE(11, c);
       tc::tc_fence_after_sync();
       float* pf = of ? of + tok0 * ((int64_t)a.Hv * D) : nullptr;
       __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
@@ -1065,22 +1084,271 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tm, 512);
   }
-  TL_END(8 + seg_idx);
 }
 
-#ifndef AVE_SEG_FIRST_DIV
-#define AVE_SEG_FIRST_DIV 16   // first range = 1/16 of the longest sequence's chunks
-#define AVE_SEG_GROWTH_X4 12   // each range 3x the one before (in quarters)
-#define AVE_SEG_MAX 8
-#endif
+// ------------------------------------------------------------------------------------------------ parts: combine and fix-up
+// Once every chain of a multi-part sequence has run, the carry buffer holds, per (sequence, value head): chain 0 = the
+// true state after part 0, chain 2p-1 = the end state Psi_p of part p's local chain, chain 2p = part p's transition
+// matrix F_p (row-major [k][d]: M_end = F_p M0 + Psi_p).
+constexpr int PACK_BYTES = 2 * D * D * 2;  // bf16 hi image | lo image of one [128][128] operand
+
+// byte offset of the 16-byte piece (8 consecutive k) of row `row` in a K-major [128 rows][128 k] bf16 operand stored as
+// two 64-wide K halves of 128-byte rows with the 128-byte swizzle (the layout tcgen05.mma reads)
+__device__ __forceinline__ uint32_t kmajor_piece_off(int row, int k8) {
+  return (uint32_t)((k8 >> 3) * 16384 + row * 128 + (((k8 & 7) ^ (row & 7)) << 4));
+}
+
+// Serial combine over the parts of one (sequence, value head, 16-column slice of d_v): M0(1) = state after part 0,
+// M0(p+1) = F_p M0(p) + Psi_p in fp32 on the CUDA cores (a few 128x128x16 products), the last one is the sequence's
+// final state.  Every M0(p) also leaves as the bf16 hi/lo operand image the fix-up kernel's MMAs read (B[d_v][k]).
+constexpr int COMBINE_COLS = 16;
+__global__ void __launch_bounds__(256)
+part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ carry,
+                    uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
+  __shared__ float cur[2][D][COMBINE_COLS];
+  const int cb = blockIdx.x, h = blockIdx.y, n = blockIdx.z, tid = threadIdx.x;
+  if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;
+  const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, nullptr);
+  if (!sp.ok || (a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen)) return;
+  const int seq_chunks = (sp.len + C - 1) / C;
+  if (seq_chunks <= plan.part_begin[1]) return;  // a plain chain: the scan wrote the final state itself
+  const int slot = a.state_indices ? a.state_indices[n] : n;
+  if (slot < 0 || slot >= a.num_slots) return;
+  int active = 1;
+  for (int p = 1; p < plan.parts; ++p) active += plan.part_begin[p] < seq_chunks ? 1 : 0;
+  const int chains = 2 * plan.parts - 1;
+  auto tile_of = [&](int chain) { return carry + (((int64_t)n * chains + chain) * a.Hv + h) * (int64_t)(D * D); };
+  {
+    const float* src = tile_of(0);
+    for (int e = tid; e < D * COMBINE_COLS; e += 256) cur[0][e / COMBINE_COLS][e % COMBINE_COLS] = src[(e / COMBINE_COLS) * D + cb * COMBINE_COLS + e % COMBINE_COLS];
+  }
+  int b = 0;
+  for (int p = 1; p < active; ++p) {
+    __syncthreads();
+    {  // operand image of M0(p): B[row = d_v][k] = M0[k][d_v]; a thread writes one 16-byte piece of the hi and of the lo image
+      const int k8 = tid >> 4, v = tid & 15;
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) split_pair(make_float2(cur[b][8 * k8 + 2 * w][v], cur[b][8 * k8 + 2 * w + 1][v]), hi[w], lo[w]);
+      uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + (p - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
+      const uint32_t off = kmajor_piece_off(cb * COMBINE_COLS + v, k8);
+      *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(img + D * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    {  // next = F_p cur + Psi_p: a thread owns one row k and eight columns
+      const int k = tid >> 1, j0 = (tid & 1) * 8;
+      const float* F = tile_of(2 * p) + (int64_t)k * D;
+      const float* Psi = tile_of(2 * p - 1) + (int64_t)k * D + cb * COMBINE_COLS + j0;
+      float acc[8];
+      {
+        const float4 p0 = *reinterpret_cast<const float4*>(Psi), p1 = *reinterpret_cast<const float4*>(Psi + 4);
+        acc[0] = p0.x; acc[1] = p0.y; acc[2] = p0.z; acc[3] = p0.w; acc[4] = p1.x; acc[5] = p1.y; acc[6] = p1.z; acc[7] = p1.w;
+      }
+#pragma unroll 4
+      for (int d4 = 0; d4 < D / 4; ++d4) {
+        const float4 f = *reinterpret_cast<const float4*>(F + 4 * d4);
+        const float fv[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 c0 = *reinterpret_cast<const float4*>(&cur[b][4 * d4 + i][j0]);
+          const float4 c1 = *reinterpret_cast<const float4*>(&cur[b][4 * d4 + i][j0 + 4]);
+          acc[0] = fmaf(fv[i], c0.x, acc[0]); acc[1] = fmaf(fv[i], c0.y, acc[1]);
+          acc[2] = fmaf(fv[i], c0.z, acc[2]); acc[3] = fmaf(fv[i], c0.w, acc[3]);
+          acc[4] = fmaf(fv[i], c1.x, acc[4]); acc[5] = fmaf(fv[i], c1.y, acc[5]);
+          acc[6] = fmaf(fv[i], c1.z, acc[6]); acc[7] = fmaf(fv[i], c1.w, acc[7]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cur[b ^ 1][k][j0 + e] = acc[e];
+    }
+    b ^= 1;
+  }
+  __syncthreads();
+  if (a.final_state != nullptr) {
+    float* dst = a.final_state + ((int64_t)slot * a.Hv + h) * (int64_t)(D * D);
+    for (int e = tid; e < D * COMBINE_COLS; e += 256) dst[(e / COMBINE_COLS) * D + cb * COMBINE_COLS + e % COMBINE_COLS] = cur[b][e / COMBINE_COLS][e % COMBINE_COLS];
+  }
+}
+
+// Fix-up of the parts after the first: for 128 tokens (two chunks of one part) of one value head,
+//   o = o_local + qt M0(part)        (qt = the transition chain's rows, [128 tokens][128 d_k] fp32)
+// as one 128x128x128 product on tcgen05 with both operands as bf16 hi+lo pairs (hi hi + hi lo + lo hi), then the gated
+// RMSNorm when a gate tensor is given, and the bf16 store.  A thread owns one token row and half of its columns.
+constexpr int FIN_THREADS = 256;
+constexpr int FIN_A_HI = 0, FIN_A_LO = 32768, FIN_B_HI = 65536, FIN_B_LO = 98304, FIN_RED = 131072, FIN_BARS = FIN_RED + 1024;
+constexpr size_t FIN_SMEM = FIN_BARS + 64 + 1024;
+__global__ void __launch_bounds__(FIN_THREADS, 1)
+part_finish_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ o_f32,
+                   const float* __restrict__ qt_f32, const uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* red = reinterpret_cast<float*>(smem + FIN_RED);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FIN_BARS);
+  uint64_t* b_bar = bars;
+  uint64_t* mma_bar = bars + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int h = blockIdx.y, n = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;
+  const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, nullptr);
+  if (!sp.ok || (a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen)) return;
+  const int seq_chunks = (sp.len + C - 1) / C;
+  const int c0 = plan.part_begin[1] + 2 * (int)blockIdx.x;  // part boundaries are even, so a pair never straddles two parts
+  if (c0 >= seq_chunks) return;
+  const int part = part_of(plan, c0);
+  const int slot = a.state_indices ? a.state_indices[n] : n;
+  const bool skipped = slot < 0 || slot >= a.num_slots;  // the scan skipped the sequence: its rows are zero
+  const int64_t tok0 = sp.t0 + (int64_t)c0 * C;
+  const int rows = min(2 * C, sp.len - c0 * C);
+
+  if (tid == 0) {
+    tc::mbar_init(b_bar, 1);
+    tc::mbar_init(mma_bar, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    if (!skipped) {
+      const uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + (part - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
+      tc::mbar_expect_tx(b_bar, PACK_BYTES);
+      tc::bulk_load(smem + FIN_B_HI, img, D * D * 2, b_bar);
+      tc::bulk_load(smem + FIN_B_LO, img + D * D * 2, D * D * 2, b_bar);
+    }
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, 128);
+  if (!skipped) {  // A operand: qt rows as bf16 hi + lo, K-major swizzled; a thread converts half a row (64 of d_k)
+    const int r = tid >> 1, kh = tid & 1;
+    const float* src = qt_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + kh * 64;
+#pragma unroll
+    for (int pc = 0; pc < 8; ++pc) {
+      float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+      if (r < rows) { x0 = *reinterpret_cast<const float4*>(src + 8 * pc); x1 = *reinterpret_cast<const float4*>(src + 8 * pc + 4); }
+      uint32_t hi[4], lo[4];
+      split_pair(make_float2(x0.x, x0.y), hi[0], lo[0]);
+      split_pair(make_float2(x0.z, x0.w), hi[1], lo[1]);
+      split_pair(make_float2(x1.x, x1.y), hi[2], lo[2]);
+      split_pair(make_float2(x1.z, x1.w), hi[3], lo[3]);
+      const uint32_t off = kmajor_piece_off(r, kh * 8 + pc);
+      *reinterpret_cast<uint4*>(smem + FIN_A_HI + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(smem + FIN_A_LO + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+  }
+  tc::fence_proxy_async_smem();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  if (warp == 0 && !skipped) {
+    const bool landed = tc::mbar_wait_warp(b_bar, 0, abort_flag);
+    if (landed && tc::elect_one()) {
+      constexpr uint32_t idesc = tc::idesc_f16(128, 128, 1, 1, false, false);
+      const uint32_t sa = tc::smem_u32(smem + FIN_A_HI), sb = tc::smem_u32(smem + FIN_B_HI);
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {  // hi hi, hi lo, lo hi
+        const uint32_t ab = sa + (t == 2 ? 32768u : 0u), bb = sb + (t == 1 ? 32768u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t ko = (uint32_t)((k >> 2) * 16384 + (k & 3) * 32);
+          tc::mma_ss(tm, tc::smem_desc_sw128(ab + ko, 16, 1024), tc::smem_desc_sw128(bb + ko, 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
+        }
+      }
+      tc::mma_commit(mma_bar);
+    }
+    __syncwarp();
+    tc::mbar_wait_warp(mma_bar, 0, abort_flag);
+  }
+  __syncthreads();
+  const bool ok = *abort_flag == 0u;
+  tc::tc_fence_after_sync();
+
+  const int quarter = warp & 3, colhalf = warp >> 2;
+  const int r = quarter * 32 + lane;
+  const bool live = r < rows;
+  float x[64];
+  if (!skipped) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t acc[32];
+      tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 64 * colhalf + 32 * half, acc);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[32 * half + i] = __uint_as_float(acc[i]);
+    }
+    const float* ol = o_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + 64 * colhalf;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live) v = *reinterpret_cast<const float4*>(ol + 4 * i);
+      x[4 * i] += v.x; x[4 * i + 1] += v.y; x[4 * i + 2] += v.z; x[4 * i + 3] += v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) x[i] = 0.f;
+  }
+  if (a.z != nullptr) {
+    const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
+    const __nv_bfloat16* zr = reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (tok0 + r) * a.z_stride_t +
+                              (int64_t)h * a.z_stride_h + 64 * colhalf;
+    float gate[64];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (live) raw = *reinterpret_cast<const uint4*>(zr + 8 * i);
+      const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        gate[8 * i + 2 * w] = silu(__uint_as_float(wds[w] << 16));
+        gate[8 * i + 2 * w + 1] = silu(__uint_as_float(wds[w] & 0xffff0000u));
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      if (gate_first) x[i] *= gate[i];
+      ss = fmaf(x[i], x[i], ss);
+    }
+    red[2 * r + colhalf] = ss;
+    __syncthreads();
+    const float rinv = rsqrtf((red[2 * r] + red[2 * r + 1]) * (1.0f / D) + a.norm_eps);
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      const float wv = a.norm_weight ? a.norm_weight[64 * colhalf + i] : 1.0f;
+      x[i] = x[i] * rinv * wv * (gate_first ? 1.0f : gate[i]);
+    }
+  }
+  if (live && ok) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (tok0 + r) * a.o_stride_t + (int64_t)h * a.o_stride_h +
+                         64 * colhalf;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
+                                                          pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
+  if (warp == 1) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tm, 128);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ schedule and scratch
+constexpr int SEG_FIRST_DIV = 16;   // first range = 1/16 of the longest chain's chunks
+constexpr int SEG_GROWTH_X4 = 12;   // each range 3x the one before (in quarters)
+constexpr int SEG_MAX = 8;
+constexpr int NUM_SMS = 148;        // B200; the schedule is a pure function of the arguments, so that the workspace
+                                    // query and the launch agree without a device being current
 struct WsLayout {
-  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, carry, total;
+  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, qt_f32, carry, m0_pack, total;
   int64_t chunks;
-  int segments;        // chunk ranges per sequence handled by separate launches
-  int seg_begin[9];    // range i covers chunks [seg_begin[i], seg_begin[i+1]) of every sequence
+  int max_chunks;      // bound of the longest sequence, in chunks
+  int parts;           // see ScanPlan
+  int part_begin[MAX_PARTS + 1];
+  int segments;        // chunk ranges handled by separate launches
+  int seg_begin[9];    // range i covers chunk offsets [seg_begin[i], seg_begin[i+1]) inside every part
 };
 
-WsLayout ws_layout(const AveGdnArgs& a) {
+// `plain`: one part, one range, everything on the caller's stream (the schedule of the fixed-scratch entry point).
+WsLayout ws_layout(const AveGdnArgs& a, bool plain) {
   WsLayout L;
   L.chunks = a.cu_seqlens ? (int64_t)a.T / C + a.n_seqs : (int64_t)a.B * ((a.T + C - 1) / C);
   const size_t recs = (size_t)L.chunks * a.Hv;
@@ -1094,39 +1362,63 @@ WsLayout ws_layout(const AveGdnArgs& a) {
   L.tu_hi = off; off = up(off + recs * REC_P);
   L.tu_lo = off; off = up(off + recs * REC_P);
   L.scal = off; off = up(off + recs * (size_t)(SCAL_FLOATS * 4));
-  L.o_f32 = off;
-  if (a.z != nullptr) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // un-normalised output for the gated norm
-  // Few long chains (fewer scan CTAs than half the SMs): cut the sequences into ranges so that pass 1 of range i+1 runs
-  // on the idle SMs while pass 2 of range i walks its chain.  The state crosses ranges through the carry buffer.
   // The longest chain is known for dense batches and for packed ones that come with the max_seqlen bound; otherwise only
-  // its bound T is.  Ranges pay off when the chains leave SMs idle: fewer chains than half the SMs.  (Also switching
-  // them on for packed batches whose longest chain exceeds 1.5 times an SM's share of all chunk-heads was measured on
-  // an eighth of the heads of the 256K-token batch, 256 chains: 1.38 ms against 1.15 ms without ranges.)
+  // its bound T is.
   const int max_chunks = ((a.cu_seqlens != nullptr && a.max_seqlen > 0 ? min(a.max_seqlen, a.T) : a.T) + C - 1) / C;
-  const bool chain_bound = (int64_t)a.n_seqs * a.Hv <= 74;
+  L.max_chunks = max_chunks;
+  const int64_t heads_total = (int64_t)a.n_seqs * a.Hv;
+  const bool push = a.o_peers != nullptr && a.n_peers > 1;
+  // Parts: with few long chains most SMs idle while every chain walks its chunks one after the other.  Cutting the
+  // sequences into S parts that run at the same time shortens the walk S-fold at the price of a second (transition)
+  // chain per later part and one GEMM-shaped fix-up; S is the largest count whose 2S-1 chains per head still get an SM
+  // each.  Not with the fused all-gather: there the fix-up would push most rows to the peers after the scan instead of
+  // beside it.
+  L.parts = 1;
+  if (!plain && !push && max_chunks >= 32) {
+    const int64_t per_head = (NUM_SMS / (heads_total > 0 ? heads_total : 1) + 1) / 2;  // chains per head that still get an SM each: 2S - 1
+    int S = per_head < MAX_PARTS ? (int)per_head : MAX_PARTS;
+    while (S > 1 && max_chunks / S < 16) --S;
+    L.parts = max(S, 1);
+  }
+  L.part_begin[0] = 0;
+  {
+    // equal parts, rounded to even chunk counts (the fix-up works on pairs of chunks)
+    const int len = ((max_chunks + L.parts - 1) / L.parts + 1) & ~1;
+    for (int p = 1; p <= MAX_PARTS; ++p) L.part_begin[p] = p < L.parts ? p * len : (1 << 24);
+  }
+  const int part_len = L.parts > 1 ? max(L.part_begin[1], max_chunks - L.part_begin[L.parts - 1]) : max_chunks;
+  L.o_f32 = off;
+  if (a.z != nullptr || L.parts > 1) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // rows waiting for the norm / the fix-up
+  L.qt_f32 = off;
+  if (L.parts > 1) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);                    // the transition chains' rows
+  // Ranges: few long chains (fewer scan CTAs than half the SMs, or parts): pass 1 of range i+1 runs on the idle SMs
+  // while pass 2 of range i walks its chains.  The state crosses ranges through the carry buffer.  (Also switching them
+  // on for packed batches whose longest chain exceeds 1.5 times an SM's share of all chunk-heads was measured on an
+  // eighth of the heads of the 256K-token batch, 256 chains: 1.38 ms against 1.15 ms without ranges.)
+  const bool chain_bound = heads_total <= 74;
   L.seg_begin[0] = 0;
-  if (!(chain_bound && max_chunks >= 32)) {
+  if (plain || !(chain_bound && max_chunks >= 32)) {
     L.segments = 1;
     L.seg_begin[1] = 1 << 24;  // every chunk (times 64 still fits an int)
   } else {
     // A short first range (its pass 1 is the only one nothing overlaps), then ranges that grow geometrically: pass 1
-    // of a range must fit inside pass 2 of the range before it, and per chunk pass 1 (on the idle SMs) is about twice
-    // as fast as the chain.
+    // of a range must fit inside pass 2 of the range before it.
     // With the fused all-gather the gated norm of a range also pushes that range's rows to every peer over NVLink,
     // which takes about as long as the chain itself; only the last range's push is exposed, so the ranges are equal
     // and as many as the event pool allows instead of growing.
-    const bool push = a.o_peers != nullptr && a.n_peers > 1;
-    int len = push ? (max_chunks + AVE_SEG_MAX - 1) / AVE_SEG_MAX : max(1, (max_chunks + AVE_SEG_FIRST_DIV - 1) / AVE_SEG_FIRST_DIV);
+    int len = push ? (part_len + SEG_MAX - 1) / SEG_MAX : max(1, (part_len + SEG_FIRST_DIV - 1) / SEG_FIRST_DIV);
     L.segments = 0;
-    while (L.seg_begin[L.segments] < max_chunks) {
+    while (L.seg_begin[L.segments] < part_len) {
       int next = L.seg_begin[L.segments] + len;
-      if (L.segments == AVE_SEG_MAX - 1 || next >= max_chunks) next = max_chunks;
+      if (L.segments == SEG_MAX - 1 || next >= part_len) next = part_len;
       L.seg_begin[++L.segments] = next;
-      if (!push) len = max(len + 1, len * AVE_SEG_GROWTH_X4 / 4);
+      if (!push) len = max(len + 1, len * SEG_GROWTH_X4 / 4);
     }
   }
   L.carry = off;
-  if (L.segments > 1) off = up(off + (size_t)a.n_seqs * a.Hv * D * D * 4);
+  if (L.segments > 1 || L.parts > 1) off = up(off + (size_t)a.n_seqs * (2 * L.parts - 1) * a.Hv * D * D * 4);
+  L.m0_pack = off;
+  if (L.parts > 1) off = up(off + (size_t)a.n_seqs * (L.parts - 1) * a.Hv * PACK_BYTES);
   L.total = off;
   return L;
 }
@@ -1136,47 +1428,58 @@ WsLayout ws_layout(const AveGdnArgs& a) {
 int launch_gated_rmsnorm_f32in_batched(const AveGdnNormArgs& a, cudaStream_t stream, const void* const* peers, int n_peers,
                                        int64_t peer_off, int batches, int64_t xs_b, int64_t zs_b, int64_t ys_b);
 
-size_t prefill_tc_workspace_bytes(const AveGdnArgs& a) { return ws_layout(a).total; }
+size_t prefill_tc_workspace_bytes(const AveGdnArgs& a, bool plain) { return ws_layout(a, plain).total; }
 
-#ifdef AVE_TRACE
-extern "C" int ave_tl_reset(void) {
-  unsigned long long init[64];
-  for (int i = 0; i < 32; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0; }
-  return (int)cudaMemcpyToSymbol(g_tl, init, sizeof(init));
-}
-extern "C" int ave_tl_read(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_tl, sizeof(unsigned long long) * 64); }
-extern "C" int ave_trace_read(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
-}
-#endif
-
-// Helper streams and events for the range-overlapped schedule, one set per device, created on first use.  Pass 2
-// runs on a high-priority stream so that, when a range's pass 1 completes and both its pass 2 and the next range's
-// pass 1 become runnable on an empty GPU, the few whole-SM pass-2 CTAs are placed first.
-struct SideStream {
+// Helper streams and events for the range-overlapped schedule.  Pass 2 runs on a high-priority stream so that, when a
+// range's pass 1 completes and both its pass 2 and the next range's pass 1 become runnable, the few whole-SM pass-2
+// CTAs are placed first.  Each device owns a small pool of such sets; a call takes the set its stream hashes to, so
+// calls on different streams usually overlap instead of queueing behind one another's helper streams.  A device's sets
+// and the whole enqueue sequence of a call are guarded by that device's mutex: the record/wait pairs of two host
+// threads never interleave, which is what makes a set shareable at all (a wait binds to the event's latest record at
+// the time of the call).
+struct SideSet {
   cudaStream_t prep = nullptr, scan = nullptr, norm = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr, join_norm = nullptr;
-  cudaEvent_t done[8] = {}, scanned[8] = {};
+  cudaEvent_t done[SEG_MAX] = {}, scanned[SEG_MAX] = {};
+  bool ready = false;
 };
-static SideStream* side_stream(int dev) {
-  static SideStream per_dev[64];
-  SideStream& s = per_dev[dev & 63];
-  if (s.prep == nullptr) {
-    int lo = 0, hi = 0;
-    if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess) return nullptr;
-    if (cudaStreamCreateWithPriority(&s.prep, cudaStreamNonBlocking, lo) != cudaSuccess) { s.prep = nullptr; return nullptr; }
-    bool ok = cudaStreamCreateWithPriority(&s.scan, cudaStreamNonBlocking, hi) == cudaSuccess;
-    ok = ok && cudaStreamCreateWithPriority(&s.norm, cudaStreamNonBlocking, lo) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&s.join_norm, cudaEventDisableTiming) == cudaSuccess;
-    for (int i = 0; i < 8; ++i) {
-      ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
-      ok = ok && cudaEventCreateWithFlags(&s.scanned[i], cudaEventDisableTiming) == cudaSuccess;
-    }
-    if (!ok) return nullptr;
+constexpr int SIDE_SETS = 4, MAX_DEVICES = 64;
+struct DeviceSide {
+  std::mutex mu;
+  SideSet sets[SIDE_SETS];
+  bool attr_set = false;
+};
+static DeviceSide g_side[MAX_DEVICES];
+
+static void destroy_side_set(SideSet& s) {
+  if (s.prep) cudaStreamDestroy(s.prep);
+  if (s.scan) cudaStreamDestroy(s.scan);
+  if (s.norm) cudaStreamDestroy(s.norm);
+  for (cudaEvent_t e : {s.fork, s.join, s.join_norm}) if (e) cudaEventDestroy(e);
+  for (int i = 0; i < SEG_MAX; ++i) { if (s.done[i]) cudaEventDestroy(s.done[i]); if (s.scanned[i]) cudaEventDestroy(s.scanned[i]); }
+  s = SideSet{};
+}
+// Called with the device's mutex held.  A set is built in a local and published only when every piece exists.
+static SideSet* side_set(DeviceSide& dev, cudaStream_t stream) {
+  SideSet& slot = dev.sets[(reinterpret_cast<uintptr_t>(stream) >> 4) % SIDE_SETS];
+  if (slot.ready) return &slot;
+  SideSet s;
+  int lo = 0, hi = 0;
+  bool ok = cudaDeviceGetStreamPriorityRange(&lo, &hi) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithPriority(&s.prep, cudaStreamNonBlocking, lo) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithPriority(&s.scan, cudaStreamNonBlocking, hi) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithPriority(&s.norm, cudaStreamNonBlocking, lo) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&s.join_norm, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; i < SEG_MAX; ++i) {
+    ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s.scanned[i], cudaEventDisableTiming) == cudaSuccess;
   }
-  return &s;
+  if (!ok) { destroy_side_set(s); return nullptr; }
+  s.ready = true;
+  slot = s;
+  return &slot;
 }
 
 // Gated RMSNorm over the fp32 output for tokens [t_begin, t_end) of every batch row, one launch.
@@ -1212,8 +1515,9 @@ static int norm_rows(const AveGdnArgs& a, float* o_f32, int t_begin, int t_end, 
   return AVE_GDN_OK;
 }
 
-int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_stream) {
-  const WsLayout L = ws_layout(a);
+// Enqueues one prefill.  Thread-safe: the enqueue sequence of a call runs under the device's mutex (see SideSet).
+int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
+  const WsLayout L = ws_layout(a, plain);
   if (L.chunks == 0 || a.n_seqs == 0) return AVE_GDN_OK;
   char* ws = reinterpret_cast<char*>(a.workspace);
   int32_t* chunk_start = reinterpret_cast<int32_t*>(ws + L.chunk_start);
@@ -1241,68 +1545,101 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
     if ((rc = make_tmap(&maps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.v), 4, dv4, sv, boxv, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
 
-  if (a.cu_seqlens != nullptr) chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, chunk_start, (int)L.chunks);
-  constexpr size_t smem_prep = PREP_SMEM;
-  static bool attr_set_dev[64] = {};
-  int dev = 0;
-  AVE_CUDA_TRY(cudaGetDevice(&dev));
-  if (!attr_set_dev[dev & 63]) {
-    AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_prep));
+  int dev_id = 0;
+  AVE_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (dev_id < 0 || dev_id >= MAX_DEVICES) return AVE_GDN_UNSUPPORTED;
+  DeviceSide& dev = g_side[dev_id];
+  std::lock_guard<std::mutex> guard(dev.mu);
+  if (!dev.attr_set) {
+    AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREP_SMEM));
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
-    attr_set_dev[dev & 63] = true;
+    AVE_CUDA_TRY(cudaFuncSetAttribute(part_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FIN_SMEM));
+    dev.attr_set = true;
   }
-  float* o_f32 = a.z ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
+  if (a.cu_seqlens != nullptr) {
+    chunk_table_tc_kernel<<<1, 1024, 0, stream>>>(a.cu_seqlens, a.n_seqs, a.T, chunk_start, (int)L.chunks, a.status);
+    AVE_CUDA_TRY(cudaGetLastError());
+  }
+  float* o_f32 = (a.z != nullptr || L.parts > 1) ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
+  float* qt_f32 = L.parts > 1 ? reinterpret_cast<float*>(ws + L.qt_f32) : nullptr;
   float* carry = reinterpret_cast<float*>(ws + L.carry);
+  uint8_t* m0_pack = reinterpret_cast<uint8_t*>(ws + L.m0_pack);
   const int32_t* seq_order = a.cu_seqlens ? chunk_start + a.n_seqs + 1 + L.chunks : nullptr;
-  const dim3 prep_grid((unsigned)L.chunks, (unsigned)a.Hv);
-  const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)a.Hv;
-  SideStream* side = (L.segments > 1 && allow_side_stream) ? side_stream(dev) : nullptr;
-  bool norm_done = a.z == nullptr;
+  ScanPlan plan;
+  plan.parts = L.parts;
+  for (int p = 0; p <= MAX_PARTS; ++p) plan.part_begin[p] = L.part_begin[p];
+  const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)(2 * L.parts - 1) * (unsigned)a.Hv;
+  const int part0_tokens = L.parts > 1 ? min(a.T, L.part_begin[1] * C) : a.T;  // tokens no fix-up touches (dense layout)
+
+  // combine + fix-up of the later parts, after every chain has finished (parts > 1 only)
+  auto finish_parts = [&](cudaStream_t s) -> int {
+    if (L.parts <= 1) return AVE_GDN_OK;
+    plan.r0 = 0; plan.rn = 1 << 24;
+    part_combine_kernel<<<dim3(D / COMBINE_COLS, (unsigned)a.Hv, (unsigned)a.n_seqs), 256, 0, s>>>(a, chunk_start, carry, m0_pack, plan);
+    AVE_CUDA_TRY(cudaGetLastError());
+    const int pairs = (L.max_chunks - L.part_begin[1] + 1) / 2;
+    if (pairs > 0) {
+      part_finish_kernel<<<dim3((unsigned)pairs, (unsigned)a.Hv, (unsigned)a.n_seqs), FIN_THREADS, FIN_SMEM, s>>>(a, chunk_start, o_f32, qt_f32, m0_pack, plan);
+      AVE_CUDA_TRY(cudaGetLastError());
+    }
+    return AVE_GDN_OK;
+  };
+
+  SideSet* side = L.segments > 1 ? side_set(dev, stream) : nullptr;
   if (side == nullptr) {
-    const int big = 1 << 24;  // every chunk of every sequence (times 64 still fits an int)
-    chunk_prep_kernel<<<prep_grid, PREP_THREADS, smem_prep, stream>>>(a, maps, chunk_start, po, 0, big, 0);
+    // one launch per pass on the caller's stream
+    plan.r0 = 0; plan.rn = 1 << 24;  // every chunk (times 64 still fits an int)
+    chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, PREP_SMEM, stream>>>(a, maps, chunk_start, po, plan, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, carry, seq_order, 0, big, 0);
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi,
+                                                                       po.tu_lo, po.scal, o_f32, qt_f32, carry, seq_order, plan);
     AVE_CUDA_TRY(cudaGetLastError());
-  } else {
-    // pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
-    // done, and (dense layouts) the gated norm of range i on a third once pass 2 of range i is done; all fork from the
-    // caller's stream and join back into it through events
-    const bool norm_per_range = a.z != nullptr && a.cu_seqlens == nullptr;
-    AVE_CUDA_TRY(cudaEventRecord(side->fork, stream));
-    AVE_CUDA_TRY(cudaStreamWaitEvent(side->prep, side->fork, 0));
-    AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->fork, 0));
-    if (norm_per_range) AVE_CUDA_TRY(cudaStreamWaitEvent(side->norm, side->fork, 0));
-    for (int i = 0; i < L.segments; ++i) {
-      const int c0 = L.seg_begin[i], cn = L.seg_begin[i + 1] - L.seg_begin[i];
-      if (cn <= 0) continue;
-      chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * cn), (unsigned)a.Hv), PREP_THREADS, smem_prep, side->prep>>>(
-          a, maps, chunk_start, po, c0, cn, 1 + i);
-      AVE_CUDA_TRY(cudaGetLastError());
-      AVE_CUDA_TRY(cudaEventRecord(side->done[i], side->prep));
-      AVE_CUDA_TRY(cudaStreamWaitEvent(side->scan, side->done[i], 0));
-      chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, carry, seq_order, c0, cn, i);
-      AVE_CUDA_TRY(cudaGetLastError());
-      if (norm_per_range) {
-        AVE_CUDA_TRY(cudaEventRecord(side->scanned[i], side->scan));
-        AVE_CUDA_TRY(cudaStreamWaitEvent(side->norm, side->scanned[i], 0));
-        const int rc = norm_rows(a, o_f32, min(a.T, c0 * C), min(a.T, (c0 + cn) * C), side->norm);
-        if (rc != AVE_GDN_OK) return rc;
-      }
+    if (a.z != nullptr) {
+      // packed layouts: the norm covers every row (rows of later parts are rewritten by the fix-up, which runs after it)
+      const int rc = norm_rows(a, o_f32, 0, a.cu_seqlens ? a.T : part0_tokens, stream);
+      if (rc != AVE_GDN_OK) return rc;
     }
-    AVE_CUDA_TRY(cudaEventRecord(side->join, side->scan));
-    AVE_CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
+    return finish_parts(stream);
+  }
+
+  // Pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
+  // done, and (dense layouts) the gated norm of part 0's rows of range i on a third once pass 2 of range i is done; all
+  // fork from the caller's stream and join back into it through events.  After an error the joins are still enqueued,
+  // so that a surrounding stream capture stays well formed.
+  const bool norm_per_range = a.z != nullptr && a.cu_seqlens == nullptr;
+  AVE_CUDA_TRY(cudaEventRecord(side->fork, stream));
+  int rc = AVE_GDN_OK;
+  auto step = [&](cudaError_t e) { if (e != cudaSuccess && rc == AVE_GDN_OK) rc = cuda_fail(e); return e == cudaSuccess; };
+  step(cudaStreamWaitEvent(side->prep, side->fork, 0));
+  step(cudaStreamWaitEvent(side->scan, side->fork, 0));
+  if (norm_per_range) step(cudaStreamWaitEvent(side->norm, side->fork, 0));
+  for (int i = 0; i < L.segments && rc == AVE_GDN_OK; ++i) {
+    plan.r0 = L.seg_begin[i]; plan.rn = L.seg_begin[i + 1] - L.seg_begin[i];
+    if (plan.rn <= 0) continue;
+    chunk_prep_kernel<<<dim3((unsigned)(a.n_seqs * L.parts * plan.rn), (unsigned)a.Hv), PREP_THREADS, PREP_SMEM, side->prep>>>(
+        a, maps, chunk_start, po, plan, 1);
+    if (!step(cudaGetLastError())) break;
+    if (!step(cudaEventRecord(side->done[i], side->prep))) break;
+    if (!step(cudaStreamWaitEvent(side->scan, side->done[i], 0))) break;
+    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo,
+                                                                           po.tu_hi, po.tu_lo, po.scal, o_f32, qt_f32, carry, seq_order, plan);
+    if (!step(cudaGetLastError())) break;
     if (norm_per_range) {
-      AVE_CUDA_TRY(cudaEventRecord(side->join_norm, side->norm));
-      AVE_CUDA_TRY(cudaStreamWaitEvent(stream, side->join_norm, 0));
-      norm_done = true;
+      if (!step(cudaEventRecord(side->scanned[i], side->scan))) break;
+      if (!step(cudaStreamWaitEvent(side->norm, side->scanned[i], 0))) break;
+      const int nrc = norm_rows(a, o_f32, min(part0_tokens, plan.r0 * C), min(part0_tokens, (plan.r0 + plan.rn) * C), side->norm);
+      if (nrc != AVE_GDN_OK && rc == AVE_GDN_OK) rc = nrc;
     }
   }
-  if (!norm_done) {
-    const int rc = norm_rows(a, o_f32, 0, a.T, stream);
-    if (rc != AVE_GDN_OK) return rc;
+  if (rc == AVE_GDN_OK) {
+    if (a.z != nullptr && !norm_per_range) rc = norm_rows(a, o_f32, 0, a.T, side->scan);  // packed layout: after the last scan
+    if (rc == AVE_GDN_OK) rc = finish_parts(side->scan);
   }
-  return AVE_GDN_OK;
+  step(cudaEventRecord(side->join, side->scan));
+  step(cudaStreamWaitEvent(stream, side->join, 0));
+  step(cudaEventRecord(side->join_norm, norm_per_range ? side->norm : side->prep));
+  step(cudaStreamWaitEvent(stream, side->join_norm, 0));
+  return rc;
 }
 
 }  // namespace ave
@@ -1315,7 +1652,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool allow_side_
 // every GPU that loads the library carries until the process exits.
 namespace ave {
 int validate_prefill_args(const AveGdnArgs* a);
-constexpr size_t kStaticScratchBytes = AVE_GDN_NOALLOC_SCRATCH_BYTES;  // 64 MiB: about 1000 chunk-heads of d = 128
+constexpr size_t kStaticScratchBytes = AVE_GDN_NOALLOC_SCRATCH_BYTES;  // 64 MiB
 }
 static __device__ __align__(256) unsigned char g_static_prefill_scratch[ave::kStaticScratchBytes];
 
@@ -1327,20 +1664,26 @@ extern "C" int ave_gdn_chunk_prefill_noalloc(const AveGdnArgs* args, void* strea
   if (rc != AVE_GDN_OK) return rc;
   if ((int64_t)args->B * args->T == 0 || args->n_seqs == 0) return AVE_GDN_OK;
   if (args->dk != 128 || args->dv != 128) return AVE_GDN_UNSUPPORTED;
-  if (prefill_tc_workspace_bytes(*args) > kStaticScratchBytes) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  // the plain schedule: one launch per pass on the caller's stream, no helper streams or events, the least scratch
+  if (prefill_tc_workspace_bytes(*args, true) > kStaticScratchBytes) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  static std::mutex mu;
   static void* scratch_of_device[64] = {};
   int dev = 0;
   AVE_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return AVE_GDN_UNSUPPORTED;
-  if (scratch_of_device[dev] == nullptr) {
-    void* p = nullptr;
-    AVE_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_prefill_scratch));
-    scratch_of_device[dev] = p;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(mu);
+    if (scratch_of_device[dev] == nullptr) {
+      void* p = nullptr;
+      AVE_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_prefill_scratch));
+      scratch_of_device[dev] = p;
+    }
+    scratch = scratch_of_device[dev];
   }
   AveGdnArgs local = *args;
-  local.workspace = scratch_of_device[dev];
+  local.workspace = scratch;
   local.workspace_bytes = kStaticScratchBytes;
   // every scratch record a launch reads is written earlier in the same launch sequence, so nothing needs clearing
-  // single-stream schedule: this variant creates no streams or events either
-  return launch_prefill_tc(local, reinterpret_cast<cudaStream_t>(stream), false);
+  return launch_prefill_tc(local, reinterpret_cast<cudaStream_t>(stream), true);
 }

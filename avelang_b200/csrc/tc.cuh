@@ -37,9 +37,6 @@ constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef AVE_SPIN_SLEEP
-    __nanosleep(AVE_SPIN_SLEEP);
-#endif
     if ((it & 63u) == 63u && *abort_flag != 0u) return false;
   }
   *abort_flag = 1u;

@@ -341,7 +341,8 @@ def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, *, out=None):
 def causal_conv1d_update(x, conv_state, weight, bias=None, state_indices=None, *, out=None):
     """Decode-time step of ``causal_conv1d_silu``: ``x`` bf16 ``[N, C]`` (one new token per sequence), ``conv_state`` bf16
     ``[slots, W-1, C]`` holding each sequence's last W-1 inputs (oldest first), updated in place; optional int32
-    ``state_indices [N]`` selects the slots (negative: skip that sequence).  Returns ``y [N, C]``."""
+    ``state_indices [N]`` selects the slots (negative: skip that sequence; beyond the pool: skip it and raise bit 1 of
+    the status word).  Returns ``y [N, C]``."""
     _req(x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_cuda and x.stride(1) == 1, "x must be a bf16 CUDA tensor [N, C]")
     N, Cn = x.shape
     W = weight.shape[1]
@@ -368,6 +369,7 @@ def causal_conv1d_update(x, conv_state, weight, bias=None, state_indices=None, *
     a.state_indices = state_indices.data_ptr() if state_indices is not None else None
     a.n_seqs, a.C, a.width, a.num_slots = N, Cn, W, conv_state.shape[0]
     a.x_stride, a.y_stride = x.stride(0), out.stride(0)
+    a.status = _status_word(x.device).data_ptr()
     with torch.cuda.device(x.device):
         rc = _lib.load().ave_gdn_conv1d_update(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "causal_conv1d_update")

@@ -10,7 +10,7 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _lib, gdn
 
 __all__ = ["gemm_pipeline_transposed_b"]
 
@@ -46,6 +46,7 @@ def gemm_pipeline_transposed_b(A: torch.Tensor, B: torch.Tensor, out: torch.Tens
     a.a, a.b, a.c = A.data_ptr(), B.data_ptr(), out.data_ptr()
     a.M, a.N, a.K = m, n, k
     a.lda, a.ldb, a.ldc = A.stride(0), B.stride(0), out.stride(0)
+    a.status = gdn._status_word(A.device).data_ptr()  # gdn.read_status() also reports a GEMM that gave up a wait
     with torch.cuda.device(A.device):
         rc = _lib.load().ave_gemm_bf16_nt(ctypes.byref(a), torch.cuda.current_stream(A.device).cuda_stream)
     _lib.check(rc, "gemm_pipeline_transposed_b")

@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define AVE_GDN_ABI_VERSION 2
+#define AVE_GDN_ABI_VERSION 3
 
 typedef enum AveGdnStatus {
   AVE_GDN_OK = 0,
@@ -146,6 +146,7 @@ typedef struct AveGemmArgs {
   void* c;
   int64_t M, N, K;
   int64_t lda, ldb, ldc; /* row strides in elements, multiples of 8 */
+  uint32_t* status;      /* optional device status word (AVE_GDN_DEV_WAIT_EXPIRED: tiles were abandoned, C is incomplete) */
 } AveGemmArgs;
 int ave_gemm_bf16_nt(const AveGemmArgs* args, void* stream);
 
@@ -166,7 +167,8 @@ int ave_gdn_conv1d_silu(const AveConvArgs* args, void* stream);
 
 /* Single-token form of the same convolution for decode: per sequence n, the last width-1 inputs live in slot
  * state_indices[n] (or n) of a pool laid out [slots][width-1][C] bf16 (oldest first, channel-contiguous); the call
- * computes y[n] = silu(bias + w . [history, x[n]]) and shifts x[n] into the history in place.  Negative index: skip. */
+ * computes y[n] = silu(bias + w . [history, x[n]]) and shifts x[n] into the history in place.  Negative index: skip
+ * (no status bit); index >= num_slots: skip and flag. */
 typedef struct AveConvUpdateArgs {
   uint32_t struct_size;
   uint32_t flags;
@@ -178,6 +180,8 @@ typedef struct AveConvUpdateArgs {
   const int32_t* state_indices; /* optional int32 [n_seqs] */
   int32_t n_seqs, C, width, num_slots;
   int64_t x_stride, y_stride;
+  uint32_t* status;           /* optional device status word: AVE_GDN_DEV_BAD_SLOT when an index is >= num_slots (that
+                                 sequence is skipped: y[n] and its history are left untouched) */
 } AveConvUpdateArgs;
 int ave_gdn_conv1d_update(const AveConvUpdateArgs* args, void* stream);
 

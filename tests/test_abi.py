@@ -45,7 +45,7 @@ def test_struct_mirrors_match_header(tmp_path):
 
 def test_status_codes_without_a_device(built_lib):
     lib = _lib.load()
-    assert lib.ave_gdn_abi_version() == 2
+    assert lib.ave_gdn_abi_version() == _lib.ABI_VERSION == 3
     assert lib.ave_gdn_status_string(0) == b"ok"
     a = _lib.GdnArgs()
     assert lib.ave_gdn_decode_step(ctypes.byref(a), None) == _lib.INVALID_ARGUMENT  # struct_size == 0

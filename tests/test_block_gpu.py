@@ -76,5 +76,8 @@ def test_block_config4_full_size_prefix_and_shard(built_lib, checker):
     ref = O.gdn_block_ref(x[2:3, :P], w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d)
     err = O.rel_l2(y[2:3, :P].float().cpu(), ref.bfloat16().float())
     assert err < 5e-3, err
+    # The shard has 16 chains, few enough that its sequences are cut into parallel parts, while the unsharded run walks
+    # 128 plain chains: the same function through two schedules, so agreement is within the output tolerance, not bitwise.
     part = GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=Hk, Hv=Hv, dk=d, dv=d, rank=5, world=8).forward_local(xg)
-    assert O.rel_l2(part.float().cpu(), y[:, :, 20:24].float().cpu()) < 1e-6
+    err = O.rel_l2(part.float().cpu(), y[:, :, 20:24].float().cpu())
+    assert err < 1e-3, err

@@ -180,24 +180,122 @@ def test_prefill_config3_varlen_sample(gdn, checker):
 
 def test_prefill_config3_full_size(gdn, checker):
     """The 256K-token packed varlen configuration at full size (64 sequences of 128..16384 tokens, nonzero initial
-    states): the shortest, the median and the longest sequence against the C checker, every state finite, and a
-    second run bit-identical (the scan walks the sequences longest first; the order must not leak into results)."""
+    states): every sequence and every final state against the C checker, and a second run bit-identical (the scan
+    walks the sequences longest first; the order must not leak into results)."""
     O, C = checker
     inp = synth.config3()
     o, s = _run(gdn, inp)
     o2, s2 = _run(gdn, inp)
     assert torch.equal(o, o2) and torch.equal(s, s2)
-    assert bool(torch.isfinite(s).all()) and bool(torch.isfinite(o.float()).all())
     cu = inp.cu_seqlens.tolist()
     lens = inp.extras["lengths"]
     assert sum(lens) == inp.q.shape[1] == cu[-1]
-    order = sorted(range(64), key=lambda n: lens[n])
-    for n in (order[0], order[32], order[-1]):
+    o_ref, s_ref = C.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, inp.initial_state, inp.cu_seqlens)
+    o_cpu, s_cpu = o.cpu(), s.cpu()
+    for n in range(64):
         a, b = cu[n], cu[n + 1]
-        o_ref, s_ref = C.recurrent(inp.q[:, a:b], inp.k[:, a:b], inp.v[:, a:b], inp.g[:, a:b], inp.beta[:, a:b], inp.scale,
-                                   inp.initial_state[n:n + 1])
-        check_o(O, o[:, a:b], o_ref)
-        check_s(O, s[n:n + 1], s_ref)
+        check_o(O, o_cpu[:, a:b], o_ref[:, a:b])
+        check_s(O, s_cpu[n:n + 1], s_ref[n:n + 1])
+    check_o(O, o_cpu, o_ref)
+    check_s(O, s_cpu, s_ref)
+
+
+@pytest.mark.parametrize("gate_scale", [1.0, 0.01, 0.001])
+@pytest.mark.parametrize("with_z", [False, True])
+def test_prefill_parallel_parts_dense(gdn, checker, gate_scale, with_z):
+    """Few long chains (2 sequences x 4 heads, 65 chunks with a ragged tail): each sequence is cut into parts that are
+    scanned at the same time (a local and a transition chain per later part), combined, and fixed up by one GEMM per
+    part.  Slow gates make the state that crosses the parts the dominant term."""
+    O, C = checker
+    T = 64 * 64 + 37
+    inp = synth.make_inputs(2, T, 2, 4, 128, 128, seed=41, with_z=with_z, n_states=2, gate_scale=gate_scale)
+    g = dev(inp)
+    o, s = gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, initial_state=g.initial_state, output_final_state=True,
+                                      z=g.z if with_z else None)
+    assert gdn.read_status() == 0
+    o_ref, s_ref = C.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, inp.initial_state)
+    if with_z:
+        o_ref = O.gated_rmsnorm(o_ref, inp.z)
+    for t0 in range(0, T, 1024):  # per stretch of tokens, so that one wrong part cannot hide in the total
+        check_o(O, o[:, t0:t0 + 1024], o_ref[:, t0:t0 + 1024])
+    check_s(O, s, s_ref)
+
+
+def test_prefill_parallel_parts_varlen_pool(gdn, checker):
+    """Packed sequences of very different lengths with pool slots: long ones are cut into parts, short ones stay plain
+    chains, one is skipped by a negative slot; with and without the max_seqlen bound."""
+    O, C = checker
+    lens = [5000, 64, 1, 2049, 3100]
+    T = sum(lens)
+    inp = synth.make_inputs(1, T, 2, 4, 128, 128, seed=43, with_z=True, n_states=8, gate_scale=0.01)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    idx = torch.tensor([6, 1, 3, -1, 0], dtype=torch.int32)
+    g = dev(inp)
+    for z in (None, g.z):
+        for bound in (None, max(lens)):
+            pool = g.initial_state.clone()
+            o, _ = gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, initial_state=pool, output_final_state=True,
+                                              cu_seqlens=cu.cuda(), state_indices=idx.cuda(), z=z, max_seqlen=bound)
+            assert gdn.read_status() == 0
+            for n, L in enumerate(lens):
+                a, b = int(cu[n]), int(cu[n + 1])
+                sl = int(idx[n])
+                if sl < 0:
+                    assert torch.count_nonzero(o[:, a:b]) == 0
+                    continue
+                o_ref, s_ref = C.recurrent(inp.q[:, a:b], inp.k[:, a:b], inp.v[:, a:b], inp.g[:, a:b], inp.beta[:, a:b], inp.scale,
+                                           inp.initial_state[sl:sl + 1])
+                check_o(O, o[:, a:b], o_ref if z is None else O.gated_rmsnorm(o_ref, inp.z[:, a:b]))
+                check_s(O, pool[sl:sl + 1], s_ref)
+            unused = [sl for sl in range(8) if sl not in idx.tolist()]
+            assert torch.equal(pool[unused].cpu(), inp.initial_state[unused])
+
+
+def test_prefill_rejects_a_non_monotone_offset_table(gdn):
+    """Offsets that are valid pair by pair but not as a whole would need more chunks than the scratch holds: the whole
+    batch is skipped and flagged, nothing is read or written out of bounds, and the next call works."""
+    inp = synth.make_inputs(1, 8192, 2, 4, 128, 128, seed=3, n_states=3)
+    g = dev(inp)
+    bad = torch.tensor([0, 5000, 3000, 8192], dtype=torch.int32, device="cuda")
+    s_in = g.initial_state.clone()
+    gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, initial_state=s_in, output_final_state=True, cu_seqlens=bad)
+    assert gdn.read_status() & 2  # AVE_GDN_DEV_BAD_SEQLEN
+    assert torch.equal(s_in, g.initial_state)
+    good = torch.tensor([0, 3000, 5000, 8192], dtype=torch.int32, device="cuda")
+    o, s = gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, initial_state=s_in, output_final_state=True, cu_seqlens=good)
+    assert gdn.read_status() == 0 and bool(torch.isfinite(o.float()).all())
+
+
+def test_prefill_two_host_threads_two_streams(gdn, checker):
+    """Two host threads enqueue range-overlapped prefills on their own streams at the same time (the schedule forks onto
+    helper streams through events): both results match the checker."""
+    import threading
+    O, C = checker
+    inps = [synth.make_inputs(1, 4096, 2, 4, 128, 128, seed=50 + i, with_z=True, n_states=1, gate_scale=0.05) for i in range(2)]
+    gs = [dev(i) for i in inps]
+    res, errs = [None, None], []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(4):
+                    res[i] = gdn.chunk_gated_delta_rule(gs[i].q, gs[i].k, gs[i].v, gs[i].g, gs[i].beta,
+                                                        initial_state=gs[i].initial_state, output_final_state=True, z=gs[i].z)
+            st.synchronize()
+        except Exception as e:  # surfaced in the main thread
+            errs.append(e)
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errs, errs
+    torch.cuda.synchronize()
+    assert gdn.read_status() == 0
+    for i in range(2):
+        o_ref, s_ref = C.recurrent(inps[i].q, inps[i].k, inps[i].v, inps[i].g, inps[i].beta, inps[i].scale, inps[i].initial_state)
+        check_o(O, res[i][0], O.gated_rmsnorm(o_ref, inps[i].z))
+        check_s(O, res[i][1], s_ref)
 
 
 def test_mixed_prefill_decode_step(gdn, checker):
