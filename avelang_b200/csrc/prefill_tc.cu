@@ -132,6 +132,13 @@ struct ScanPlan {
   int part_begin[MAX_PARTS + 1];  // part_begin[parts] = 1 << 24
   int r0, rn;
 };
+constexpr int PACK_BYTES = 2 * 128 * 128 * 2;  // bf16 hi image | lo image of one [128][128] operand
+constexpr int QT_BYTES = 2 * 128 * 64 * 2;     // bf16 hi image | lo image of one chunk's qt^T [128 d_k][64 tokens]
+// byte offset of the 16-byte piece (8 consecutive k) of row `row` in a K-major [128 rows][128 k] bf16 operand stored as
+// two 64-wide K halves of 128-byte rows with the 128-byte swizzle (the layout tcgen05.mma reads)
+__device__ __forceinline__ uint32_t kmajor_piece_off(int row, int k8) {
+  return (uint32_t)((k8 >> 3) * 16384 + row * 128 + (((k8 & 7) ^ (row & 7)) << 4));
+}
 __device__ __forceinline__ int part_of(const ScanPlan& pl, int cis) {
   int p = 0;
 #pragma unroll
@@ -683,8 +690,9 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
                      const __nv_bfloat16* __restrict__ p_hi_ws, const __nv_bfloat16* __restrict__ p_lo_ws,
                      const __nv_bfloat16* __restrict__ tu_hi_ws, const __nv_bfloat16* __restrict__ tu_lo_ws,
-                     const float* __restrict__ scal_ws, float* __restrict__ o_f32, float* __restrict__ qt_f32,
-                     float* __restrict__ carry, const int32_t* __restrict__ seq_order, const __grid_constant__ ScanPlan plan) {
+                     const float* __restrict__ scal_ws, float* __restrict__ o_f32, uint8_t* __restrict__ qt_img,
+                     float* __restrict__ carry, uint8_t* __restrict__ m0_pack, const int32_t* __restrict__ seq_order,
+                     const __grid_constant__ ScanPlan plan) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
@@ -748,9 +756,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
     }
   }
   __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (int64_t)h * a.o_stride_h;
-  // where this chain's per-token rows go: the transition chain's qt rows and the local rows of later parts wait in fp32
-  // scratch for the fix-up; part 0 writes fp32 scratch only when a gated norm follows, else the result itself
-  float* const out_f32 = phi ? qt_f32 : ((a.z != nullptr || part > 0) ? o_f32 : nullptr);
+  // where this chain's per-token rows go: the local rows of later parts wait in fp32 scratch for the fix-up; part 0
+  // writes fp32 scratch only when a gated norm follows, else the result itself; the transition chain's rows leave as
+  // the bf16 hi/lo operand images the fix-up's MMAs read (see the output warps)
+  float* const out_f32 = (!phi && (a.z != nullptr || part > 0)) ? o_f32 : nullptr;
   if (slot < 0) {  // skipped sequence: zero output, no state access (chain 0 clears the whole sequence once)
     if (chain > 0 || plan.r0 > 0) return;
     float* zf = a.z != nullptr ? o_f32 : nullptr;
@@ -1012,6 +1021,19 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         state_out[(int64_t)(64 * grp + 2 * w + 1) * D + d] = Hreg[w].y;
       }
     }
+    if (alive && multi && chain == 0 && c_hi == part_end) {
+      // the state that enters part 1, as the fix-up's B operand image (row = d_v, K = d_k): this thread's row, 8 pieces
+      uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) split_pair(Hreg[4 * j + w], hi[w], lo[w]);
+        const uint32_t off = kmajor_piece_off(d, 8 * grp + j);
+        *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(img + D * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+    }
   } else {
     tc::reg_set<REGS_OUT, 128>();
     // ------------------------------------------------------------------ output warps: o = scale (qs_i O1 + O2), straight
@@ -1035,42 +1057,55 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
       const int64_t fstep = (int64_t)a.Hv * D, bstep = a.o_stride_t;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t o1[32], o2[32];
-        tc::tmem_ld32(lane_addr + TM_O1 + 32 * part, o1);
-        tc::tmem_ld32(lane_addr + TM_O2 + 32 * part, o2);
+      for (int part = 0; part < 4; ++part) {  // 16 tokens at a time: keeps this warpgroup inside its register budget
+        uint32_t o1[16], o2[16];
+        tc::tmem_ld16(lane_addr + TM_O1 + 16 * part, o1);
+        tc::tmem_ld16(lane_addr + TM_O2 + 16 * part, o2);
         tc::tmem_ld_wait();
-        if (part == 1) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
+        if (part == 3) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
           tc::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
         }
-        float ov[32];
+        float ov[16];
 #pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          const float4 qs = *reinterpret_cast<const float4*>(scal + 32 * part + 4 * j4);
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 qs = *reinterpret_cast<const float4*>(scal + 16 * part + 4 * j4);
           const float2 r0 = __ffma2_rn(make_float2(qs.x, qs.y), make_float2(__uint_as_float(o1[4 * j4]), __uint_as_float(o1[4 * j4 + 1])),
                                        make_float2(__uint_as_float(o2[4 * j4]), __uint_as_float(o2[4 * j4 + 1])));
           const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o1[4 * j4 + 3])),
                                        make_float2(__uint_as_float(o2[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 3])));
           ov[4 * j4 + 0] = r0.x; ov[4 * j4 + 1] = r0.y; ov[4 * j4 + 2] = r1.x; ov[4 * j4 + 3] = r1.y;
         }
-        const int n_here = min(32, len - 32 * part);  // tokens of this half that exist
-        if (pf != nullptr) {
-          if (n_here == 32) {
+        const int n_here = min(16, len - 16 * part);  // tokens of this quarter that exist
+        if (phi) {
+          // qt^T of this chunk as bf16 hi and lo images [128 d_k rows][64 tokens] with the 128-byte swizzle: the fix-up
+          // reads them, unchanged, as the MN-major A operand of its MMA.  This thread owns row d: two 16-byte pieces.
+          uint8_t* img = qt_img + ((int64_t)(c_first + c) * a.Hv + h) * (int64_t)QT_BYTES + d * 128;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { *pf = ov[j]; pf += fstep; }
+          for (int half = 0; half < 2; ++half) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) split_pair(make_float2(ov[8 * half + 2 * w], ov[8 * half + 2 * w + 1]), hi[w], lo[w]);
+            const uint32_t off = (uint32_t)(((2 * part + half) ^ (d & 7)) << 4);
+            *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(img + C * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          }
+        } else if (pf != nullptr) {
+          if (n_here == 16) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { *pf = ov[j]; pf += fstep; }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { if (j < n_here) *pf = ov[j]; pf += fstep; }
+            for (int j = 0; j < 16; ++j) { if (j < n_here) *pf = ov[j]; pf += fstep; }
           }
         } else {
-          if (n_here == 32) {
+          if (n_here == 16) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { *pb = __float2bfloat16(ov[j]); pb += bstep; }
+            for (int j = 0; j < 16; ++j) { *pb = __float2bfloat16(ov[j]); pb += bstep; }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { if (j < n_here) *pb = __float2bfloat16(ov[j]); pb += bstep; }
+            for (int j = 0; j < 16; ++j) { if (j < n_here) *pb = __float2bfloat16(ov[j]); pb += bstep; }
           }
         }
       }
@@ -1090,17 +1125,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 // Once every chain of a multi-part sequence has run, the carry buffer holds, per (sequence, value head): chain 0 = the
 // true state after part 0, chain 2p-1 = the end state Psi_p of part p's local chain, chain 2p = part p's transition
 // matrix F_p (row-major [k][d]: M_end = F_p M0 + Psi_p).
-constexpr int PACK_BYTES = 2 * D * D * 2;  // bf16 hi image | lo image of one [128][128] operand
-
-// byte offset of the 16-byte piece (8 consecutive k) of row `row` in a K-major [128 rows][128 k] bf16 operand stored as
-// two 64-wide K halves of 128-byte rows with the 128-byte swizzle (the layout tcgen05.mma reads)
-__device__ __forceinline__ uint32_t kmajor_piece_off(int row, int k8) {
-  return (uint32_t)((k8 >> 3) * 16384 + row * 128 + (((k8 & 7) ^ (row & 7)) << 4));
-}
-
 // Serial combine over the parts of one (sequence, value head, 16-column slice of d_v): M0(1) = state after part 0,
-// M0(p+1) = F_p M0(p) + Psi_p in fp32 on the CUDA cores (a few 128x128x16 products), the last one is the sequence's
-// final state.  Every M0(p) also leaves as the bf16 hi/lo operand image the fix-up kernel's MMAs read (B[d_v][k]).
+// M0(p+1) = F_p M0(p) + Psi_p in fp32 on the CUDA cores (a few 128x128x16 products); the last one is the sequence's
+// final state.  M0(p) for p >= 2 also leaves as the bf16 hi/lo operand image the fix-up kernel's MMAs read (B[d_v][k]);
+// the image of M0(1) was written by the scan itself.
 constexpr int COMBINE_COLS = 16;
 __global__ void __launch_bounds__(256)
 part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ carry,
@@ -1116,6 +1144,7 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
   if (slot < 0 || slot >= a.num_slots) return;
   int active = 1;
   for (int p = 1; p < plan.parts; ++p) active += plan.part_begin[p] < seq_chunks ? 1 : 0;
+  if (active == 2 && a.final_state == nullptr) return;  // nothing to produce
   const int chains = 2 * plan.parts - 1;
   auto tile_of = [&](int chain) { return carry + (((int64_t)n * chains + chain) * a.Hv + h) * (int64_t)(D * D); };
   {
@@ -1125,16 +1154,6 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
   int b = 0;
   for (int p = 1; p < active; ++p) {
     __syncthreads();
-    {  // operand image of M0(p): B[row = d_v][k] = M0[k][d_v]; a thread writes one 16-byte piece of the hi and of the lo image
-      const int k8 = tid >> 4, v = tid & 15;
-      uint32_t hi[4], lo[4];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) split_pair(make_float2(cur[b][8 * k8 + 2 * w][v], cur[b][8 * k8 + 2 * w + 1][v]), hi[w], lo[w]);
-      uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + (p - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
-      const uint32_t off = kmajor_piece_off(cb * COMBINE_COLS + v, k8);
-      *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(img + D * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    }
     {  // next = F_p cur + Psi_p: a thread owns one row k and eight columns
       const int k = tid >> 1, j0 = (tid & 1) * 8;
       const float* F = tile_of(2 * p) + (int64_t)k * D;
@@ -1144,7 +1163,7 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
         const float4 p0 = *reinterpret_cast<const float4*>(Psi), p1 = *reinterpret_cast<const float4*>(Psi + 4);
         acc[0] = p0.x; acc[1] = p0.y; acc[2] = p0.z; acc[3] = p0.w; acc[4] = p1.x; acc[5] = p1.y; acc[6] = p1.z; acc[7] = p1.w;
       }
-#pragma unroll 4
+#pragma unroll 8
       for (int d4 = 0; d4 < D / 4; ++d4) {
         const float4 f = *reinterpret_cast<const float4*>(F + 4 * d4);
         const float fv[4] = {f.x, f.y, f.z, f.w};
@@ -1162,6 +1181,17 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
       for (int e = 0; e < 8; ++e) cur[b ^ 1][k][j0 + e] = acc[e];
     }
     b ^= 1;
+    __syncthreads();
+    if (p + 1 < active) {  // operand image of M0(p+1): B[row = d_v][k] = M0[k][d_v]; one 16-byte piece of hi and lo per thread
+      const int k8 = tid >> 4, v = tid & 15;
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) split_pair(make_float2(cur[b][8 * k8 + 2 * w][v], cur[b][8 * k8 + 2 * w + 1][v]), hi[w], lo[w]);
+      uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + p) * a.Hv + h) * (int64_t)PACK_BYTES;
+      const uint32_t off = kmajor_piece_off(cb * COMBINE_COLS + v, k8);
+      *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(img + D * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
   }
   __syncthreads();
   if (a.final_state != nullptr) {
@@ -1170,164 +1200,189 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
   }
 }
 
-// Fix-up of the parts after the first: for 128 tokens (two chunks of one part) of one value head,
-//   o = o_local + qt M0(part)        (qt = the transition chain's rows, [128 tokens][128 d_k] fp32)
-// as one 128x128x128 product on tcgen05 with both operands as bf16 hi+lo pairs (hi hi + hi lo + lo hi), then the gated
-// RMSNorm when a gate tensor is given, and the bf16 store.  A thread owns one token row and half of its columns.
-constexpr int FIN_THREADS = 256;
-constexpr int FIN_A_HI = 0, FIN_A_LO = 32768, FIN_B_HI = 65536, FIN_B_LO = 98304, FIN_RED = 131072, FIN_BARS = FIN_RED + 1024;
+// Fix-up of the parts after the first.  For 128 tokens (two chunks of one part) of one value head,
+//   o = o_local + qt M0(part)        (qt = the transition chain's rows, [128 tokens][128 d_k])
+// is one 128x128x128 product on tcgen05 with both operands as bf16 hi+lo pairs (hi hi + hi lo + lo hi): A = the qt^T
+// images the scan wrote (MN-major, brought in by bulk copies), B = the image of M0(part).  Then the gated RMSNorm when a
+// gate tensor is given, and the bf16 store.  A CTA serves one (sequence, part, head) and walks every `gridDim.x`-th
+// pair of chunks with B resident: while the threads finish pair i (a thread owns one token row and a quarter of its
+// columns), the product of pair i+1 already runs into the second accumulator and the images of pair i+2 are in flight.
+constexpr int FIN_THREADS = 512;
+constexpr int FIN_A = 0, FIN_A_STAGE = 65536, FIN_B = 2 * FIN_A_STAGE, FIN_RED = FIN_B + PACK_BYTES, FIN_BARS = FIN_RED + 2048;
 constexpr size_t FIN_SMEM = FIN_BARS + 64 + 1024;
 __global__ void __launch_bounds__(FIN_THREADS, 1)
 part_finish_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ o_f32,
-                   const float* __restrict__ qt_f32, const uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
+                   const uint8_t* __restrict__ qt_img, const uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(smem + FIN_RED);
+  float* red = reinterpret_cast<float*>(smem + FIN_RED);  // [128 rows][4 column quarters]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FIN_BARS);
   uint64_t* b_bar = bars;
-  uint64_t* mma_bar = bars + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* a_full = bars + 1;   // [2]
+  uint64_t* mma_bar = bars + 3;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  const int h = blockIdx.y, n = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.z / (plan.parts - 1), part = 1 + blockIdx.z % (plan.parts - 1);
   if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;
   const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, nullptr);
   if (!sp.ok || (a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen)) return;
   const int seq_chunks = (sp.len + C - 1) / C;
-  const int c0 = plan.part_begin[1] + 2 * (int)blockIdx.x;  // part boundaries are even, so a pair never straddles two parts
-  if (c0 >= seq_chunks) return;
-  const int part = part_of(plan, c0);
+  const int c_begin = plan.part_begin[part], c_end = min(plan.part_begin[part + 1], seq_chunks);
+  const int n_pairs = (c_end - c_begin + 1) / 2;  // part boundaries are even, so a pair never straddles two parts
+  if ((int)blockIdx.x >= n_pairs) return;
   const int slot = a.state_indices ? a.state_indices[n] : n;
   const bool skipped = slot < 0 || slot >= a.num_slots;  // the scan skipped the sequence: its rows are zero
-  const int64_t tok0 = sp.t0 + (int64_t)c0 * C;
-  const int rows = min(2 * C, sp.len - c0 * C);
+  const int64_t rec0 = a.cu_seqlens ? chunk_start[n] : (int64_t)n * ((a.T + C - 1) / C);  // record of the sequence's chunk 0
+  const int stride = gridDim.x;
 
+  auto load_a = [&](int pair, int stage) {  // called by one thread
+    const int c0 = c_begin + 2 * pair, cnt = min(2, c_end - c0);
+    uint8_t* dst = smem + FIN_A + stage * FIN_A_STAGE;
+    tc::mbar_expect_tx(&a_full[stage], (uint32_t)(cnt * QT_BYTES));
+    for (int i = 0; i < cnt; ++i) {
+      const uint8_t* img = qt_img + ((rec0 + c0 + i) * a.Hv + h) * (int64_t)QT_BYTES;
+      tc::bulk_load(dst + i * 16384, img, 16384, &a_full[stage]);                   // hi: [chunk 0 | chunk 1]
+      tc::bulk_load(dst + 32768 + i * 16384, img + 16384, 16384, &a_full[stage]);   // lo: [chunk 0 | chunk 1]
+    }
+  };
+  // warp 0: waits for pair number `it` of this CTA to land and issues its product into accumulator it & 1
+  auto issue_pair = [&](int it, uint32_t tm) -> bool {
+    const int stage = it & 1;
+    bool landed = it > 0 || tc::mbar_wait_warp(b_bar, 0, abort_flag);
+    landed = landed && tc::mbar_wait_warp(&a_full[stage], (uint32_t)(it >> 1) & 1u, abort_flag);
+    tc::tc_fence_after_sync();
+    if (landed && tc::elect_one()) {
+      constexpr uint32_t idesc = tc::idesc_f16(128, 128, 1, 1, true, false);  // A MN-major (token rows), B K-major
+      const uint32_t sa = tc::smem_u32(smem + FIN_A + stage * FIN_A_STAGE), sb = tc::smem_u32(smem + FIN_B);
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {  // hi hi, hi lo, lo hi
+        const uint32_t ab = sa + (t == 2 ? 32768u : 0u), bb = sb + (t == 1 ? 32768u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // 16 d_k rows of qt^T per step: 2048 bytes; the two chunks' images lie 16384 bytes apart
+          tc::mma_ss(tm + 128u * (uint32_t)stage, tc::smem_desc_sw128(ab + k * 2048, 16384, 1024),
+                     tc::smem_desc_sw128(bb + (uint32_t)((k >> 2) * 16384 + (k & 3) * 32), 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
+      }
+      tc::mma_commit(&mma_bar[stage]);
+    }
+    __syncwarp();
+    return landed;
+  };
   if (tid == 0) {
     tc::mbar_init(b_bar, 1);
-    tc::mbar_init(mma_bar, 1);
+    tc::mbar_init(&a_full[0], 1);
+    tc::mbar_init(&a_full[1], 1);
+    tc::mbar_init(&mma_bar[0], 1);
+    tc::mbar_init(&mma_bar[1], 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     if (!skipped) {
       const uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + (part - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
       tc::mbar_expect_tx(b_bar, PACK_BYTES);
-      tc::bulk_load(smem + FIN_B_HI, img, D * D * 2, b_bar);
-      tc::bulk_load(smem + FIN_B_LO, img + D * D * 2, D * D * 2, b_bar);
+      tc::bulk_load(smem + FIN_B, img, PACK_BYTES, b_bar);
+      load_a(blockIdx.x, 0);
+      if ((int)blockIdx.x + stride < n_pairs) load_a(blockIdx.x + stride, 1);
     }
   }
-  if (warp == 1) tc::tmem_alloc(tmem_slot, 128);
-  if (!skipped) {  // A operand: qt rows as bf16 hi + lo, K-major swizzled; a thread converts half a row (64 of d_k)
-    const int r = tid >> 1, kh = tid & 1;
-    const float* src = qt_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + kh * 64;
-#pragma unroll
-    for (int pc = 0; pc < 8; ++pc) {
-      float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
-      if (r < rows) { x0 = *reinterpret_cast<const float4*>(src + 8 * pc); x1 = *reinterpret_cast<const float4*>(src + 8 * pc + 4); }
-      uint32_t hi[4], lo[4];
-      split_pair(make_float2(x0.x, x0.y), hi[0], lo[0]);
-      split_pair(make_float2(x0.z, x0.w), hi[1], lo[1]);
-      split_pair(make_float2(x1.x, x1.y), hi[2], lo[2]);
-      split_pair(make_float2(x1.z, x1.w), hi[3], lo[3]);
-      const uint32_t off = kmajor_piece_off(r, kh * 8 + pc);
-      *reinterpret_cast<uint4*>(smem + FIN_A_HI + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(smem + FIN_A_LO + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    }
-  }
-  tc::fence_proxy_async_smem();
+  if (warp == 1) tc::tmem_alloc(tmem_slot, 256);
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  if (warp == 0 && !skipped) {
-    const bool landed = tc::mbar_wait_warp(b_bar, 0, abort_flag);
-    if (landed && tc::elect_one()) {
-      constexpr uint32_t idesc = tc::idesc_f16(128, 128, 1, 1, false, false);
-      const uint32_t sa = tc::smem_u32(smem + FIN_A_HI), sb = tc::smem_u32(smem + FIN_B_HI);
+  const int quarter = warp & 3, colq = warp >> 2;  // TMEM lane quarter (token rows) and column quarter of this warp
+  const int r = quarter * 32 + lane;
+  bool ok = true;
+  if (warp == 0 && !skipped) issue_pair(0, tm);
+
+  int it = 0;
+  for (int pair = blockIdx.x; pair < n_pairs && ok; pair += stride, ++it) {
+    const int stage = it & 1;
+    const int c0 = c_begin + 2 * pair;
+    const int64_t tok0 = sp.t0 + (int64_t)c0 * C;
+    const int rows = min(min(2, c_end - c0) * C, sp.len - c0 * C);
+    const bool live = r < rows;
+    // the next pair's product runs while this pair is finished (its accumulator was drained an iteration ago)
+    if (warp == 0 && !skipped && pair + stride < n_pairs) issue_pair(it + 1, tm);
+    // rows this thread adds and gates
+    float x[32];
+    uint4 zraw[4];
+    if (!skipped && live) {
+      const float* ol = o_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + 32 * colq;
 #pragma unroll
-      for (int t = 0; t < 3; ++t) {  // hi hi, hi lo, lo hi
-        const uint32_t ab = sa + (t == 2 ? 32768u : 0u), bb = sb + (t == 1 ? 32768u : 0u);
+      for (int i = 0; i < 8; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(ol + 4 * i);
+        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+      }
+    } else {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t ko = (uint32_t)((k >> 2) * 16384 + (k & 3) * 32);
-          tc::mma_ss(tm, tc::smem_desc_sw128(ab + ko, 16, 1024), tc::smem_desc_sw128(bb + ko, 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
+      for (int i = 0; i < 32; ++i) x[i] = 0.f;
+    }
+    if (a.z != nullptr) {
+      const __nv_bfloat16* zr = reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (tok0 + r) * a.z_stride_t +
+                                (int64_t)h * a.z_stride_h + 32 * colq;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) zraw[i] = live ? *reinterpret_cast<const uint4*>(zr + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (!skipped) {
+      ok = tc::mbar_wait(&mma_bar[stage], (uint32_t)(it >> 1) & 1u, abort_flag);
+      tc::tc_fence_after_sync();
+      // this pair's images have been read: their stage takes the images of the pair after the next
+      if (ok && tid == 0 && pair + 2 * stride < n_pairs) load_a(pair + 2 * stride, stage);
+      if (ok) {
+        uint32_t acc[32];
+        tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 128u * (uint32_t)stage + 32 * colq, acc);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] += __uint_as_float(acc[i]);
+      }
+    }
+    if (a.z != nullptr) {
+      const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
+      float gate[32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t wds[4] = {zraw[i].x, zraw[i].y, zraw[i].z, zraw[i].w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          gate[8 * i + 2 * w] = silu(__uint_as_float(wds[w] << 16));
+          gate[8 * i + 2 * w + 1] = silu(__uint_as_float(wds[w] & 0xffff0000u));
         }
       }
-      tc::mma_commit(mma_bar);
-    }
-    __syncwarp();
-    tc::mbar_wait_warp(mma_bar, 0, abort_flag);
-  }
-  __syncthreads();
-  const bool ok = *abort_flag == 0u;
-  tc::tc_fence_after_sync();
-
-  const int quarter = warp & 3, colhalf = warp >> 2;
-  const int r = quarter * 32 + lane;
-  const bool live = r < rows;
-  float x[64];
-  if (!skipped) {
+      float ss = 0.f;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t acc[32];
-      tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 64 * colhalf + 32 * half, acc);
-      tc::tmem_ld_wait();
+      for (int i = 0; i < 32; ++i) {
+        if (gate_first) x[i] *= gate[i];
+        ss = fmaf(x[i], x[i], ss);
+      }
+      red[4 * r + colq] = ss;
+      __syncthreads();
+      const float4 s4 = *reinterpret_cast<const float4*>(red + 4 * r);
+      const float rinv = rsqrtf((s4.x + s4.y + s4.z + s4.w) * (1.0f / D) + a.norm_eps);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) x[32 * half + i] = __uint_as_float(acc[i]);
-    }
-    const float* ol = o_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + 64 * colhalf;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (live) v = *reinterpret_cast<const float4*>(ol + 4 * i);
-      x[4 * i] += v.x; x[4 * i + 1] += v.y; x[4 * i + 2] += v.z; x[4 * i + 3] += v.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 64; ++i) x[i] = 0.f;
-  }
-  if (a.z != nullptr) {
-    const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
-    const __nv_bfloat16* zr = reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (tok0 + r) * a.z_stride_t +
-                              (int64_t)h * a.z_stride_h + 64 * colhalf;
-    float gate[64];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (live) raw = *reinterpret_cast<const uint4*>(zr + 8 * i);
-      const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        gate[8 * i + 2 * w] = silu(__uint_as_float(wds[w] << 16));
-        gate[8 * i + 2 * w + 1] = silu(__uint_as_float(wds[w] & 0xffff0000u));
+      for (int i = 0; i < 32; ++i) {
+        const float wv = a.norm_weight ? a.norm_weight[32 * colq + i] : 1.0f;
+        x[i] *= rinv * wv * (gate_first ? 1.0f : gate[i]);
       }
     }
-    float ss = 0.f;
+    if (live && ok) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (tok0 + r) * a.o_stride_t + (int64_t)h * a.o_stride_h +
+                           32 * colq;
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      if (gate_first) x[i] *= gate[i];
-      ss = fmaf(x[i], x[i], ss);
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
+                                                            pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
     }
-    red[2 * r + colhalf] = ss;
-    __syncthreads();
-    const float rinv = rsqrtf((red[2 * r] + red[2 * r + 1]) * (1.0f / D) + a.norm_eps);
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      const float wv = a.norm_weight ? a.norm_weight[64 * colhalf + i] : 1.0f;
-      x[i] = x[i] * rinv * wv * (gate_first ? 1.0f : gate[i]);
-    }
-  }
-  if (live && ok) {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (tok0 + r) * a.o_stride_t + (int64_t)h * a.o_stride_h +
-                         64 * colhalf;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
-                                                          pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
+    // this pair's accumulator is free once every thread has read its part of the product
+    tc::tc_fence_before_sync();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    tc::tc_fence_after_sync();
   }
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (!ok && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
+  if (*abort_flag != 0u && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
   if (warp == 1) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tm, 128);
+    tc::tmem_dealloc(tm, 256);
   }
 }
 
@@ -1335,10 +1390,11 @@ part_finish_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, 
 constexpr int SEG_FIRST_DIV = 16;   // first range = 1/16 of the longest chain's chunks
 constexpr int SEG_GROWTH_X4 = 12;   // each range 3x the one before (in quarters)
 constexpr int SEG_MAX = 8;
+constexpr int PART0_X4 = 4;         // length of part 0 in quarters of a later part's length
 constexpr int NUM_SMS = 148;        // B200; the schedule is a pure function of the arguments, so that the workspace
                                     // query and the launch agree without a device being current
 struct WsLayout {
-  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, qt_f32, carry, m0_pack, total;
+  size_t chunk_start, w_hi, w_lo, p_hi, p_lo, tu_hi, tu_lo, scal, o_f32, qt_img, carry, m0_pack, total;
   int64_t chunks;
   int max_chunks;      // bound of the longest sequence, in chunks
   int parts;           // see ScanPlan
@@ -1382,15 +1438,18 @@ WsLayout ws_layout(const AveGdnArgs& a, bool plain) {
   }
   L.part_begin[0] = 0;
   {
-    // equal parts, rounded to even chunk counts (the fix-up works on pairs of chunks)
-    const int len = ((max_chunks + L.parts - 1) / L.parts + 1) & ~1;
-    for (int p = 1; p <= MAX_PARTS; ++p) L.part_begin[p] = p < L.parts ? p * len : (1 << 24);
+    // Part 0 runs one chain and needs no fix-up, a later part runs two chains and its rows wait for the fix-up, so
+    // part 0 is made PART0_X4 / 4 times as long as the others; lengths are even (the fix-up works on pairs of chunks).
+    const int len = max(2, (4 * max_chunks / (4 * (L.parts - 1) + PART0_X4) + 1) & ~1);
+    const int first = L.parts > 1 ? max(2, (max_chunks - (L.parts - 1) * len + 1) & ~1) : 0;
+    for (int p = 1; p <= MAX_PARTS; ++p) L.part_begin[p] = p < L.parts ? first + (p - 1) * len : (1 << 24);
   }
-  const int part_len = L.parts > 1 ? max(L.part_begin[1], max_chunks - L.part_begin[L.parts - 1]) : max_chunks;
+  int part_len = 0;  // the longest part, in chunks
+  for (int p = 0; p < L.parts; ++p) part_len = max(part_len, min(L.part_begin[p + 1], max_chunks) - L.part_begin[p]);
   L.o_f32 = off;
   if (a.z != nullptr || L.parts > 1) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);  // rows waiting for the norm / the fix-up
-  L.qt_f32 = off;
-  if (L.parts > 1) off = up(off + (size_t)a.B * a.T * a.Hv * D * 4);                    // the transition chains' rows
+  L.qt_img = off;
+  if (L.parts > 1) off = up(off + recs * (size_t)QT_BYTES);                             // the transition chains' rows (operand images)
   // Ranges: few long chains (fewer scan CTAs than half the SMs, or parts): pass 1 of range i+1 runs on the idle SMs
   // while pass 2 of range i walks its chains.  The state crosses ranges through the carry buffer.  (Also switching them
   // on for packed batches whose longest chain exceeds 1.5 times an SM's share of all chunk-heads was measured on an
@@ -1439,7 +1498,7 @@ size_t prefill_tc_workspace_bytes(const AveGdnArgs& a, bool plain) { return ws_l
 // the time of the call).
 struct SideSet {
   cudaStream_t prep = nullptr, scan = nullptr, norm = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr, join_norm = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr, join_norm = nullptr, chains_done = nullptr, combined = nullptr;
   cudaEvent_t done[SEG_MAX] = {}, scanned[SEG_MAX] = {};
   bool ready = false;
 };
@@ -1455,7 +1514,7 @@ static void destroy_side_set(SideSet& s) {
   if (s.prep) cudaStreamDestroy(s.prep);
   if (s.scan) cudaStreamDestroy(s.scan);
   if (s.norm) cudaStreamDestroy(s.norm);
-  for (cudaEvent_t e : {s.fork, s.join, s.join_norm}) if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : {s.fork, s.join, s.join_norm, s.chains_done, s.combined}) if (e) cudaEventDestroy(e);
   for (int i = 0; i < SEG_MAX; ++i) { if (s.done[i]) cudaEventDestroy(s.done[i]); if (s.scanned[i]) cudaEventDestroy(s.scanned[i]); }
   s = SideSet{};
 }
@@ -1472,6 +1531,8 @@ static SideSet* side_set(DeviceSide& dev, cudaStream_t stream) {
   ok = ok && cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&s.join_norm, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&s.chains_done, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&s.combined, cudaEventDisableTiming) == cudaSuccess;
   for (int i = 0; i < SEG_MAX; ++i) {
     ok = ok && cudaEventCreateWithFlags(&s.done[i], cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&s.scanned[i], cudaEventDisableTiming) == cudaSuccess;
@@ -1561,7 +1622,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     AVE_CUDA_TRY(cudaGetLastError());
   }
   float* o_f32 = (a.z != nullptr || L.parts > 1) ? reinterpret_cast<float*>(ws + L.o_f32) : nullptr;
-  float* qt_f32 = L.parts > 1 ? reinterpret_cast<float*>(ws + L.qt_f32) : nullptr;
+  uint8_t* qt_img = L.parts > 1 ? reinterpret_cast<uint8_t*>(ws + L.qt_img) : nullptr;
   float* carry = reinterpret_cast<float*>(ws + L.carry);
   uint8_t* m0_pack = reinterpret_cast<uint8_t*>(ws + L.m0_pack);
   const int32_t* seq_order = a.cu_seqlens ? chunk_start + a.n_seqs + 1 + L.chunks : nullptr;
@@ -1571,17 +1632,33 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
   const unsigned scan_grid = (unsigned)a.n_seqs * (unsigned)(2 * L.parts - 1) * (unsigned)a.Hv;
   const int part0_tokens = L.parts > 1 ? min(a.T, L.part_begin[1] * C) : a.T;  // tokens no fix-up touches (dense layout)
 
-  // combine + fix-up of the later parts, after every chain has finished (parts > 1 only)
-  auto finish_parts = [&](cudaStream_t s) -> int {
+  // combine + fix-up of the later parts, after every chain has finished (parts > 1 only).  The image of M0(1) comes from
+  // the scan, so with two parts the fix-up needs nothing from the combine, which then only produces the final states
+  // and runs on `side_stream` (when given) beside the fix-up.
+  auto finish_parts = [&](cudaStream_t s, cudaStream_t side_stream, cudaEvent_t scanned, cudaEvent_t combined) -> int {
     if (L.parts <= 1) return AVE_GDN_OK;
     plan.r0 = 0; plan.rn = 1 << 24;
-    part_combine_kernel<<<dim3(D / COMBINE_COLS, (unsigned)a.Hv, (unsigned)a.n_seqs), 256, 0, s>>>(a, chunk_start, carry, m0_pack, plan);
-    AVE_CUDA_TRY(cudaGetLastError());
-    const int pairs = (L.max_chunks - L.part_begin[1] + 1) / 2;
-    if (pairs > 0) {
-      part_finish_kernel<<<dim3((unsigned)pairs, (unsigned)a.Hv, (unsigned)a.n_seqs), FIN_THREADS, FIN_SMEM, s>>>(a, chunk_start, o_f32, qt_f32, m0_pack, plan);
+    const dim3 cgrid(D / COMBINE_COLS, (unsigned)a.Hv, (unsigned)a.n_seqs);
+    const bool beside = L.parts == 2 && side_stream != nullptr;
+    if (beside) {
+      AVE_CUDA_TRY(cudaEventRecord(scanned, s));
+      AVE_CUDA_TRY(cudaStreamWaitEvent(side_stream, scanned, 0));
+      part_combine_kernel<<<cgrid, 256, 0, side_stream>>>(a, chunk_start, carry, m0_pack, plan);
+      AVE_CUDA_TRY(cudaGetLastError());
+      AVE_CUDA_TRY(cudaEventRecord(combined, side_stream));
+    } else {
+      part_combine_kernel<<<cgrid, 256, 0, s>>>(a, chunk_start, carry, m0_pack, plan);
       AVE_CUDA_TRY(cudaGetLastError());
     }
+    int part_len = 0;  // the longest of the later parts
+    for (int p = 1; p < L.parts; ++p) part_len = max(part_len, min(L.part_begin[p + 1], L.max_chunks) - L.part_begin[p]);
+    const int64_t groups = (int64_t)a.n_seqs * (L.parts - 1) * a.Hv;
+    int split = (int)(NUM_SMS / (groups > 0 ? groups : 1));  // CTAs per (sequence, part, head): about one wave of the SMs
+    split = max(1, min(split, (part_len + 1) / 2));
+    part_finish_kernel<<<dim3((unsigned)split, (unsigned)a.Hv, (unsigned)(a.n_seqs * (L.parts - 1))), FIN_THREADS, FIN_SMEM, s>>>(
+        a, chunk_start, o_f32, qt_img, m0_pack, plan);
+    AVE_CUDA_TRY(cudaGetLastError());
+    if (beside) AVE_CUDA_TRY(cudaStreamWaitEvent(s, combined, 0));
     return AVE_GDN_OK;
   };
 
@@ -1592,14 +1669,14 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, PREP_SMEM, stream>>>(a, maps, chunk_start, po, plan, 0);
     AVE_CUDA_TRY(cudaGetLastError());
     chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi,
-                                                                       po.tu_lo, po.scal, o_f32, qt_f32, carry, seq_order, plan);
+                                                                       po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
     AVE_CUDA_TRY(cudaGetLastError());
     if (a.z != nullptr) {
       // packed layouts: the norm covers every row (rows of later parts are rewritten by the fix-up, which runs after it)
       const int rc = norm_rows(a, o_f32, 0, a.cu_seqlens ? a.T : part0_tokens, stream);
       if (rc != AVE_GDN_OK) return rc;
     }
-    return finish_parts(stream);
+    return finish_parts(stream, nullptr, nullptr, nullptr);
   }
 
   // Pass 1 of all ranges back to back on one helper stream, pass 2 of range i on a second once pass 1 of range i is
@@ -1622,7 +1699,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     if (!step(cudaEventRecord(side->done[i], side->prep))) break;
     if (!step(cudaStreamWaitEvent(side->scan, side->done[i], 0))) break;
     chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo,
-                                                                           po.tu_hi, po.tu_lo, po.scal, o_f32, qt_f32, carry, seq_order, plan);
+                                                                           po.tu_hi, po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
     if (!step(cudaGetLastError())) break;
     if (norm_per_range) {
       if (!step(cudaEventRecord(side->scanned[i], side->scan))) break;
@@ -1633,7 +1710,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
   }
   if (rc == AVE_GDN_OK) {
     if (a.z != nullptr && !norm_per_range) rc = norm_rows(a, o_f32, 0, a.T, side->scan);  // packed layout: after the last scan
-    if (rc == AVE_GDN_OK) rc = finish_parts(side->scan);
+    if (rc == AVE_GDN_OK) rc = finish_parts(side->scan, side->prep, side->chains_done, side->combined);
   }
   step(cudaEventRecord(side->join, side->scan));
   step(cudaStreamWaitEvent(stream, side->join, 0));
