@@ -63,6 +63,7 @@ class GateArgs(ctypes.Structure):
 SYMBOLS = {
     "ave_gdn_chunk_prefill": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_prefill_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(GdnArgs)]),
+    "ave_gdn_prefill_launch_count": (ctypes.c_int, [ctypes.POINTER(GdnArgs)]),
     "ave_gdn_chunk_prefill_noalloc": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_decode_step": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_gated_rmsnorm": (ctypes.c_int, [ctypes.POINTER(NormArgs), P]),

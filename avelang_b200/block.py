@@ -85,9 +85,11 @@ class GdnBlockShard:
         self.dt_bias = dt_bias[vh.start:vh.stop].float().to(device).contiguous()
         self.norm_weight = None if norm_weight is None else norm_weight.float().to(device).contiguous()
 
-    def forward_local(self, x: torch.Tensor, cu_seqlens=None, out=None, out_peers=None) -> torch.Tensor:
+    def forward_local(self, x: torch.Tensor, cu_seqlens=None, out=None, out_peers=None, keep: dict | None = None) -> torch.Tensor:
         """x: bf16 [B, T, hidden] (replicated on every rank).  Returns this rank's normalised head outputs
-        [B, T, Hv/G, dv] (written into ``out`` / scattered to ``out_peers`` when given)."""
+        [B, T, Hv/G, dv] (written into ``out`` / scattered to ``out_peers`` when given).  ``keep``: a dict that receives
+        the delta-rule stage's own inputs (q, k, v after the convolution, g, beta, z), so that a test can hold that
+        stage alone against the checker."""
         from . import gdn, gemm
         B, T, hidden = x.shape
         y2 = gemm.gemm_pipeline_transposed_b(x.reshape(B * T, hidden), self.w)
@@ -103,6 +105,8 @@ class GdnBlockShard:
         v = qkv[:, :, nq + nk:].reshape(B, T, self.hv_local, self.dv)
         g, beta = gdn.gate_beta(a_in, b_in, self.A_log, self.dt_bias)
         g, beta = g.reshape(B, T, self.hv_local), beta.reshape(B, T, self.hv_local)
+        if keep is not None:
+            keep.update(q=q, k=k, v=v, g=g, beta=beta, z=z)
         o, _ = gdn.chunk_gated_delta_rule(q, k, v, g, beta, use_qk_l2norm_in_kernel=True, cu_seqlens=cu_seqlens,
                                           z=z, norm_weight=self.norm_weight, out=out, out_peers=out_peers)
         return o

@@ -10,6 +10,7 @@ int launch_prefill_simt(const AveGdnArgs& a, cudaStream_t stream);
 size_t prefill_simt_workspace_bytes(const AveGdnArgs& a);
 int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain);
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a, bool plain);
+int prefill_tc_launch_count(const AveGdnArgs& a, bool plain);
 int launch_gated_rmsnorm(const AveGdnNormArgs& a, cudaStream_t stream);
 int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
@@ -78,6 +79,13 @@ const char* ave_gdn_status_string(int status) {
 size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args) {
   if (validate_gdn(args, true) != AVE_GDN_OK) return 0;
   return prefill_ws_bytes(*args);
+}
+
+int ave_gdn_prefill_launch_count(const AveGdnArgs* args) {
+  if (validate_gdn(args, true) != AVE_GDN_OK) return 0;
+  if ((int64_t)args->B * args->T == 0 || args->n_seqs == 0) return 0;
+  if (args->dk == 128) return prefill_tc_launch_count(*args, false);
+  return (args->cu_seqlens ? 1 : 0) + 2 + (args->z ? 1 : 0);  // chunk table, two passes, gated norm
 }
 
 int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream) {

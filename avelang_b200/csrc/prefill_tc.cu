@@ -1489,6 +1489,19 @@ int launch_gated_rmsnorm_f32in_batched(const AveGdnNormArgs& a, cudaStream_t str
 
 size_t prefill_tc_workspace_bytes(const AveGdnArgs& a, bool plain) { return ws_layout(a, plain).total; }
 
+// Kernels one call enqueues, mirroring launch_prefill_tc below.
+int prefill_tc_launch_count(const AveGdnArgs& a, bool plain) {
+  const WsLayout L = ws_layout(a, plain);
+  if (L.chunks == 0 || a.n_seqs == 0) return 0;
+  const bool push = a.o_peers != nullptr && a.n_peers > 1;
+  const int norm_launch = (push || a.B == 1) ? 1 : a.B;  // norm_rows: one launch, or one per batch row
+  int n = a.cu_seqlens != nullptr ? 1 : 0;                 // chunk table
+  n += 2 * L.segments;                                     // pass 1 and pass 2 of every range
+  if (a.z != nullptr) n += (a.cu_seqlens == nullptr ? L.segments : 1) * norm_launch;
+  if (L.parts > 1) n += 2;                                 // combine and fix-up
+  return n;
+}
+
 // Helper streams and events for the range-overlapped schedule.  Pass 2 runs on a high-priority stream so that, when a
 // range's pass 1 completes and both its pass 2 and the next range's pass 1 become runnable, the few whole-SM pass-2
 // CTAs are placed first.  Each device owns a small pool of such sets; a call takes the set its stream hashes to, so

@@ -21,11 +21,10 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _lib, torch_ops
 
-__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "gated_rmsnorm", "causal_conv1d_silu",
-           "causal_conv1d_update", "gate_beta",
-           "read_status"]
+__all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "mixed_prefill_decode_step", "gated_rmsnorm",
+           "causal_conv1d_silu", "causal_conv1d_update", "gate_beta", "prefill_launch_count", "read_status"]
 
 _status_words: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -117,7 +116,7 @@ def _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_sta
             setattr(a, f"{name}_stride_t", t.stride(1))
             setattr(a, f"{name}_stride_h", t.stride(2))
     a.g_stride_b, a.g_stride_t = g.stride(0), g.stride(1)
-    a.scale = float(dk ** -0.5 if scale is None else scale)
+    a.scale = float(scale)
     a.norm_eps = float(norm_eps)
     return a
 
@@ -193,15 +192,29 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     norm_weight = _prep_norm_weight(norm_weight, z, dv, q.device)
     final, num_slots = _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, q.device,
                                     output_final_state, inplace_state)
-    flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
-    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
-                   state_indices, num_slots, n_seqs, flags)
-    if max_seqlen is not None and cu_seqlens is not None:
-        a.max_seqlen = min(int(max_seqlen), T)
     if out_peers is not None:
         _req(z is not None, "out_peers needs z (the stores are fused into the gated norm)")
         _req(out_peers.dtype == torch.int64 and out_peers.dim() == 1 and out_peers.device == q.device and out_peers.is_contiguous(),
              f"out_peers must be a contiguous 1-D int64 tensor on {q.device}")
+    bound = min(int(max_seqlen), T) if (max_seqlen is not None and cu_seqlens is not None) else 0
+    torch_ops.op("chunk_prefill")(q, k, v, g, beta, o, float(dk ** -0.5 if scale is None else scale), initial_state, final,
+                                  cu_seqlens, state_indices, z, norm_weight, float(norm_eps), bool(use_qk_l2norm_in_kernel),
+                                  bound, out_peers)
+    return o, final
+
+
+@torch_ops.implement("chunk_prefill")
+def _chunk_prefill(q, k, v, g, beta, out, scale, initial_state, final_state, cu_seqlens, state_indices, z, norm_weight,
+                   norm_eps, qk_l2norm, max_seqlen, out_peers):
+    """torch.ops.avelang_gdn.chunk_prefill: fills the C argument block and calls ave_gdn_chunk_prefill on the current
+    stream, with scratch taken from the per-(device, stream) workspace this layer owns."""
+    n_seqs = q.shape[0] if cu_seqlens is None else cu_seqlens.numel() - 1
+    pool = final_state if final_state is not None else initial_state
+    num_slots = pool.shape[0] if pool is not None else n_seqs
+    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, out, scale, initial_state, final_state, cu_seqlens,
+                   state_indices, num_slots, n_seqs, _lib.FLAG_QK_L2NORM if qk_l2norm else 0)
+    a.max_seqlen = int(max_seqlen)
+    if out_peers is not None:
         a.o_peers, a.n_peers = out_peers.data_ptr(), out_peers.numel()
     lib = _lib.load()
     with torch.cuda.device(q.device):
@@ -210,7 +223,31 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         rc = lib.ave_gdn_chunk_prefill(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "chunk_gated_delta_rule")
-    return o, final
+
+
+def prefill_launch_count(q, k, v, *, z=None, cu_seqlens=None, max_seqlen=None, push=False) -> int:
+    """Number of kernels one ``chunk_gated_delta_rule`` call on tensors of these shapes enqueues (``push``: with the
+    fused all-gather).  Asked from the library, which derives it from the same schedule it launches."""
+    B, T, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    n_seqs = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    a = _lib.GdnArgs()
+    a.struct_size = ctypes.sizeof(_lib.GdnArgs)
+    # only shapes, strides and the presence of optional tensors enter the count: nothing is read through the pointers
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), v.data_ptr()
+    a.g = a.beta = v.data_ptr()
+    a.z = z.data_ptr() if z is not None else None
+    a.cu_seqlens = cu_seqlens.data_ptr() if cu_seqlens is not None else None
+    a.B, a.T, a.Hk, a.Hv, a.dk, a.dv, a.n_seqs, a.num_slots, a.chunk = B, T, Hk, Hv, dk, dv, n_seqs, n_seqs, 64
+    for name, t in (("q", q), ("k", k), ("v", v), ("z", z), ("o", v)):
+        if t is not None:
+            setattr(a, f"{name}_stride_b", t.stride(0)); setattr(a, f"{name}_stride_t", t.stride(1)); setattr(a, f"{name}_stride_h", t.stride(2))
+    a.g_stride_b, a.g_stride_t = T * Hv, Hv
+    if max_seqlen is not None and cu_seqlens is not None:
+        a.max_seqlen = min(int(max_seqlen), T)
+    if push:
+        a.o_peers, a.n_peers = v.data_ptr(), 2  # only their presence matters for the count
+    return int(_lib.load().ave_gdn_prefill_launch_count(ctypes.byref(a)))
 
 
 def fused_recurrent_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
@@ -225,13 +262,23 @@ def fused_recurrent_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state
     norm_weight = _prep_norm_weight(norm_weight, z, dv, q.device)
     final, num_slots = _prep_states(initial_state, state_indices, n_seqs, Hv, dk, dv, q.device,
                                     output_final_state, inplace_state)
-    flags = _lib.FLAG_QK_L2NORM if use_qk_l2norm_in_kernel else 0
-    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, o, scale, initial_state, final, cu_seqlens,
-                   state_indices, num_slots, n_seqs, flags)
+    torch_ops.op("decode_step")(q, k, v, g, beta, o, float(dk ** -0.5 if scale is None else scale), initial_state, final,
+                                cu_seqlens, state_indices, z, norm_weight, float(norm_eps), bool(use_qk_l2norm_in_kernel))
+    return o, final
+
+
+@torch_ops.implement("decode_step")
+def _decode_step(q, k, v, g, beta, out, scale, initial_state, final_state, cu_seqlens, state_indices, z, norm_weight,
+                 norm_eps, qk_l2norm):
+    """torch.ops.avelang_gdn.decode_step -> ave_gdn_decode_step on the current stream."""
+    n_seqs = q.shape[0] if cu_seqlens is None else cu_seqlens.numel() - 1
+    pool = final_state if final_state is not None else initial_state
+    num_slots = pool.shape[0] if pool is not None else n_seqs
+    a = _fill_args(q, k, v, g, beta, z, norm_weight, norm_eps, out, scale, initial_state, final_state, cu_seqlens,
+                   state_indices, num_slots, n_seqs, _lib.FLAG_QK_L2NORM if qk_l2norm else 0)
     with torch.cuda.device(q.device):
         rc = _lib.load().ave_gdn_decode_step(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "fused_recurrent_gated_delta_rule")
-    return o, final
 
 
 def mixed_prefill_decode_step(q, k, v, g, beta, cu_seqlens, n_decode, state_pool, state_indices, scale=None,
@@ -281,23 +328,29 @@ def gated_rmsnorm(x, z, weight=None, eps=1e-6, *, gate_first=False, out=None):
     _req(y3.data_ptr() == out.data_ptr(), "out must be viewable as [rows, H, d] without a copy")
     for t in (x3, z3, y3):
         _req(t.stride(-1) == 1, "tensors must be contiguous in their last dimension")
-    a = _lib.NormArgs()
-    a.struct_size = ctypes.sizeof(_lib.NormArgs)
-    a.flags = _lib.FLAG_GATE_FIRST if gate_first else 0
-    a.x, a.z, a.y = x3.data_ptr(), z3.data_ptr(), y3.data_ptr()
     w = None
     if weight is not None:
         _req(weight.numel() == d and weight.device == x.device, f"weight must have {d} elements on {x.device}")
         w = weight.detach().float().contiguous()
-        a.weight = w.data_ptr()
-    a.rows, a.d, a.heads, a.eps = x3.shape[0] * H, d, H, float(eps)
+    torch_ops.op("gated_rmsnorm")(x3, z3, w, float(eps), bool(gate_first), y3)
+    return out
+
+
+@torch_ops.implement("gated_rmsnorm")
+def _gated_rmsnorm(x3, z3, weight, eps, gate_first, y3):
+    """torch.ops.avelang_gdn.gated_rmsnorm -> ave_gdn_gated_rmsnorm; tensors are [rows, H, d] views."""
+    a = _lib.NormArgs()
+    a.struct_size = ctypes.sizeof(_lib.NormArgs)
+    a.flags = _lib.FLAG_GATE_FIRST if gate_first else 0
+    a.x, a.z, a.y = x3.data_ptr(), z3.data_ptr(), y3.data_ptr()
+    a.weight = weight.data_ptr() if weight is not None else None
+    a.rows, a.d, a.heads, a.eps = x3.shape[0] * x3.shape[1], x3.shape[2], x3.shape[1], float(eps)
     a.x_stride_t, a.x_stride_h = x3.stride(0), x3.stride(1)
     a.z_stride_t, a.z_stride_h = z3.stride(0), z3.stride(1)
     a.y_stride_t, a.y_stride_h = y3.stride(0), y3.stride(1)
-    with torch.cuda.device(x.device):
-        rc = _lib.load().ave_gdn_gated_rmsnorm(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
+    with torch.cuda.device(x3.device):
+        rc = _lib.load().ave_gdn_gated_rmsnorm(ctypes.byref(a), torch.cuda.current_stream(x3.device).cuda_stream)
     _lib.check(rc, "gated_rmsnorm")
-    return out
 
 
 def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, *, out=None):
@@ -322,20 +375,28 @@ def causal_conv1d_silu(x, weight, bias=None, cu_seqlens=None, *, out=None):
     _req(out.shape == x.shape and out.dtype == torch.bfloat16 and out.device == x.device and out.stride(2) == 1,
          f"out must be a bf16 tensor of shape {tuple(x.shape)} on {x.device}")
     _req(out.data_ptr() != x.data_ptr(), "out must not alias x (later tokens read earlier inputs)")
+    if cu_seqlens is not None:
+        _req(B == 1 and cu_seqlens.dtype == torch.int32 and cu_seqlens.device == x.device and cu_seqlens.is_contiguous(),
+             "cu_seqlens must be a contiguous int32 tensor on the device of x, with B == 1")
+    torch_ops.op("conv1d_silu")(x, weight, bias, cu_seqlens, out)
+    return out
+
+
+@torch_ops.implement("conv1d_silu")
+def _conv1d_silu(x, weight, bias, cu_seqlens, out):
+    """torch.ops.avelang_gdn.conv1d_silu -> ave_gdn_conv1d_silu."""
+    B, T, Cn = x.shape
     a = _lib.ConvArgs()
     a.struct_size = ctypes.sizeof(_lib.ConvArgs)
     a.x, a.w, a.y = x.data_ptr(), weight.data_ptr(), out.data_ptr()
     a.bias = bias.data_ptr() if bias is not None else None
-    a.B, a.T, a.C, a.width = B, T, Cn, W
+    a.B, a.T, a.C, a.width = B, T, Cn, weight.shape[1]
     if cu_seqlens is not None:
-        _req(B == 1 and cu_seqlens.dtype == torch.int32 and cu_seqlens.device == x.device and cu_seqlens.is_contiguous(),
-             "cu_seqlens must be a contiguous int32 tensor on the device of x, with B == 1")
         a.cu_seqlens, a.n_seqs = cu_seqlens.data_ptr(), cu_seqlens.numel() - 1
     a.x_stride_b, a.x_stride_t, a.y_stride_b, a.y_stride_t = x.stride(0), x.stride(1), out.stride(0), out.stride(1)
     with torch.cuda.device(x.device):
         rc = _lib.load().ave_gdn_conv1d_silu(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "causal_conv1d_silu")
-    return out
 
 
 def causal_conv1d_update(x, conv_state, weight, bias=None, state_indices=None, *, out=None):
@@ -362,18 +423,26 @@ def causal_conv1d_update(x, conv_state, weight, bias=None, state_indices=None, *
         out = torch.empty((N, Cn), dtype=torch.bfloat16, device=x.device)
     _req(out.shape == x.shape and out.dtype == torch.bfloat16 and out.device == x.device and out.stride(1) == 1,
          f"out must be a bf16 tensor of shape {tuple(x.shape)} on {x.device}")
+    bias = bias.contiguous() if bias is not None else None
+    torch_ops.op("conv1d_update")(x, conv_state, weight, bias, state_indices, out)
+    return out
+
+
+@torch_ops.implement("conv1d_update")
+def _conv1d_update(x, conv_state, weight, bias, state_indices, out):
+    """torch.ops.avelang_gdn.conv1d_update -> ave_gdn_conv1d_update (history updated in place)."""
+    N, Cn = x.shape
     a = _lib.ConvUpdateArgs()
     a.struct_size = ctypes.sizeof(_lib.ConvUpdateArgs)
     a.x, a.w, a.y, a.conv_state = x.data_ptr(), weight.data_ptr(), out.data_ptr(), conv_state.data_ptr()
-    a.bias = bias.contiguous().data_ptr() if bias is not None else None
+    a.bias = bias.data_ptr() if bias is not None else None
     a.state_indices = state_indices.data_ptr() if state_indices is not None else None
-    a.n_seqs, a.C, a.width, a.num_slots = N, Cn, W, conv_state.shape[0]
+    a.n_seqs, a.C, a.width, a.num_slots = N, Cn, weight.shape[1], conv_state.shape[0]
     a.x_stride, a.y_stride = x.stride(0), out.stride(0)
     a.status = _status_word(x.device).data_ptr()
     with torch.cuda.device(x.device):
         rc = _lib.load().ave_gdn_conv1d_update(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "causal_conv1d_update")
-    return out
 
 
 def gate_beta(a_in, b_in, A_log, dt_bias):
@@ -388,12 +457,18 @@ def gate_beta(a_in, b_in, A_log, dt_bias):
     _req(A_log.numel() == Hv and dt_bias.numel() == Hv and A_log.device == a_in.device, f"A_log and dt_bias must have {Hv} elements")
     g = torch.empty(a_in.shape, dtype=torch.float32, device=a_in.device)
     beta = torch.empty_like(g)
+    torch_ops.op("gate_beta")(a2, b2, A_log, dt_bias, g, beta)
+    return g, beta
+
+
+@torch_ops.implement("gate_beta")
+def _gate_beta(a2, b2, A_log, dt_bias, g, beta):
+    """torch.ops.avelang_gdn.gate_beta -> ave_gdn_gate_beta; a2, b2 are [rows, Hv] views."""
     s = _lib.GateArgs()
     s.struct_size = ctypes.sizeof(_lib.GateArgs)
     s.a, s.b, s.A_log, s.dt_bias, s.g, s.beta = (a2.data_ptr(), b2.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(),
                                                  g.data_ptr(), beta.data_ptr())
-    s.rows, s.Hv, s.a_stride_row, s.b_stride_row = a2.shape[0], Hv, a2.stride(0), b2.stride(0)
-    with torch.cuda.device(a_in.device):
-        rc = _lib.load().ave_gdn_gate_beta(ctypes.byref(s), torch.cuda.current_stream(a_in.device).cuda_stream)
+    s.rows, s.Hv, s.a_stride_row, s.b_stride_row = a2.shape[0], a2.shape[1], a2.stride(0), b2.stride(0)
+    with torch.cuda.device(a2.device):
+        rc = _lib.load().ave_gdn_gate_beta(ctypes.byref(s), torch.cuda.current_stream(a2.device).cuda_stream)
     _lib.check(rc, "gate_beta")
-    return g, beta

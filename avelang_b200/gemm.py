@@ -10,7 +10,7 @@ import ctypes
 
 import torch
 
-from . import _lib, gdn
+from . import _lib, gdn, torch_ops
 
 __all__ = ["gemm_pipeline_transposed_b"]
 
@@ -41,13 +41,19 @@ def gemm_pipeline_transposed_b(A: torch.Tensor, B: torch.Tensor, out: torch.Tens
         raise ValueError(f"out must be on device {A.device}, got {out.device}.")
     elif out.stride(1) != 1:
         raise ValueError("out must be contiguous in its last dimension.")
+    torch_ops.op("gemm_bf16_nt")(A, B, out)
+    return out
+
+
+@torch_ops.implement("gemm_bf16_nt")
+def _gemm_bf16_nt(A, B, out):
+    """torch.ops.avelang_gdn.gemm_bf16_nt -> ave_gemm_bf16_nt on the current stream."""
     a = _lib.GemmArgs()
     a.struct_size = ctypes.sizeof(_lib.GemmArgs)
     a.a, a.b, a.c = A.data_ptr(), B.data_ptr(), out.data_ptr()
-    a.M, a.N, a.K = m, n, k
+    a.M, a.N, a.K = A.shape[0], B.shape[0], A.shape[1]
     a.lda, a.ldb, a.ldc = A.stride(0), B.stride(0), out.stride(0)
     a.status = gdn._status_word(A.device).data_ptr()  # gdn.read_status() also reports a GEMM that gave up a wait
     with torch.cuda.device(A.device):
         rc = _lib.load().ave_gemm_bf16_nt(ctypes.byref(a), torch.cuda.current_stream(A.device).cuda_stream)
     _lib.check(rc, "gemm_pipeline_transposed_b")
-    return out

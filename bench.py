@@ -10,9 +10,13 @@ recurrence), so the job is N sequences and `value` is their total tokens per sec
 torchrun each rank reads RANK/LOCAL_RANK/WORLD_SIZE; rank 0 prints ONE JSON line.
 
 Extra objects on the same line: `decode` (continuous-batch decode step over a 512-slot fp32 state pool: state
-GB/s against the HBM roofline), `roofline`, `cpu_baseline`, `e2e`, `clocks`.
+GB/s against the HBM roofline), `roofline`, `cpu_baseline`, `e2e`, `clocks`, and, at the end of the line, the two
+sharded workloads timed over the same N ranks with a parity object each: `varlen` (64 packed sequences, 262144
+tokens, value heads sharded Hv/N per rank, no collective: strong scaling) and `block` (the whole GDN block, B=4,
+T=32768, heads sharded, head outputs all-gathered: by peer stores fused into the norm kernel, and by NCCL).
 `--impl reference` times the CPU restatement of the recurrence on the host cores instead (the reference
-project has no implementation of this path, so the restatement is the only CPU arm there is).
+project has no implementation of this path, so the restatement is the only CPU arm there is); with `--gpus N`
+it times the same N sequences the GPU arm processes.
 """
 from __future__ import annotations
 
@@ -52,13 +56,23 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
 
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
     def __enter__(self):
+        """Starts the sampler and waits (up to 3 s) for its first sample, so that the samples that follow fall inside
+        the region the caller is about to run: nvidia-smi takes longer to start than a short timed region lasts."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "10"],
+                                          "--format=csv,noheader,nounits", "-lms", "5"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            t0 = time.perf_counter()
+            while not self.lines and time.perf_counter() - t0 < 3.0 and self.proc.poll() is None:
+                time.sleep(0.005)
+            self.lines.clear()  # what was sampled before the load started does not count
         except OSError:
             self.proc = None
         return self
@@ -89,6 +103,33 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def bind_host_to_gpu_node(local_rank: int) -> dict:
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off (read from sysfs), before any pinned host
+    buffer is allocated, so that the end-to-end copies of N ranks do not all cross one socket's memory.  Reports what
+    it found; does nothing when the box has one node or hides the topology."""
+    info = {"numa_node": None, "cpus": None}
+    try:
+        bus = subprocess.run(["nvidia-smi", "-i", str(local_rank), "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if bus.startswith("00000000:"):
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        info["numa_node"] = node
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        if node >= 0 and len(nodes) > 1:
+            cpus = set()
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                info["cpus"] = len(cpus)
+    except (OSError, ValueError, subprocess.SubprocessError):
+        pass
+    return info
 
 
 def dist_setup(n_gpus: int):
@@ -144,8 +185,9 @@ def bench_prefill(args, rank, world):
     def step():
         return gdn.chunk_gated_delta_rule(g.q, g.k, g.v, g.g, g.beta, output_final_state=True, z=g.z, out=out)
 
-    with ClockSampler(torch.cuda.current_device()) as clocks:
-        total_ms = time_steps(step, args.steps, args.warmup, world, flush)
+    clocks = ClockSampler(torch.cuda.current_device())
+    clocks.__enter__()  # stays up through warm-up, the timed region and the end-to-end leg below
+    total_ms = time_steps(step, args.steps, args.warmup, world, flush)
     total_ms = max_over_ranks(total_ms, world)
     ms = total_ms / args.steps
 
@@ -194,9 +236,32 @@ def bench_prefill(args, rank, world):
     t1.record()
     barrier(world)
     e2e_ms = max_over_ranks(t0.elapsed_time(t1) / e2e_steps, world)
+    clocks.__exit__(None, None, None)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = o_host.numel() * o_host.element_size() + s_host.numel() * s_host.element_size()
-    return ms, clocks.summary(), e2e_ms, h2d, d2h
+
+    # the three legs one at a time (all ranks at once, max over ranks): names the leg that saturates as N grows
+    def leg(fn, reps=3):
+        fn(); barrier(world)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record(); barrier(world)
+        return max_over_ranks(a.elapsed_time(b) / reps, world)
+
+    def copy_in():
+        for k in host:
+            dev[0][k].copy_(host[k], non_blocking=True)
+
+    def copy_out():
+        o_host.copy_(outs[0], non_blocking=True)
+        s_host.copy_(states[0], non_blocking=True)
+
+    legs = {"h2d_ms": leg(copy_in), "kernels_ms": leg(step), "d2h_ms": leg(copy_out)}
+    legs["h2d_GBps_per_rank"] = h2d / (legs["h2d_ms"] * 1e-3) / 1e9
+    legs["d2h_GBps_per_rank"] = d2h / (legs["d2h_ms"] * 1e-3) / 1e9
+    return ms, clocks.summary(), e2e_ms, h2d, d2h, legs, gdn.prefill_launch_count(g.q, g.k, g.v, z=g.z)
 
 
 def bench_decode(steps=1000, warmup=20):
@@ -227,12 +292,13 @@ def bench_decode(steps=1000, warmup=20):
     return us, state_bytes, state_bytes + other
 
 
-def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0):
+def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0, n_seqs=1):
     """The C restatement of the token recurrence (fp32, OpenMP over sequence x head) on the host cores; repeated
-    until about `budget_s` seconds of CPU work have been timed (or `reps` runs)."""
+    until about `budget_s` seconds of CPU work have been timed (or `reps` runs).  `n_seqs` sequences per run (the
+    batch an N-GPU job processes per step)."""
     from avelang_b200 import synth
     from oracle import c_oracle
-    inp = synth.config1(T=sample_tokens)
+    inp = synth.make_inputs(n_seqs, sample_tokens, HK, HV, D, D, seed=0, with_z=True)
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     cores = c_oracle.set_threads(cores) or 1  # all the cores this process may use, whatever OMP_NUM_THREADS the launcher set
     t = time.perf_counter()
@@ -245,9 +311,9 @@ def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0):
         c_oracle.recurrent(inp.q, inp.k, inp.v, inp.g, inp.beta, inp.scale, precision="f32")
         times.append(time.perf_counter() - t)
     sec = statistics.median(times)
-    return {"value": sample_tokens / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"full workload (T={sample_tokens}, 32 value heads, d=128), fp32 token recurrence in C with "
-                      f"OpenMP, median of {reps} runs, {sec:.3f} s each"}
+    return {"value": n_seqs * sample_tokens / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"full workload ({n_seqs} x T={sample_tokens}, 32 value heads, d=128), fp32 token recurrence in C "
+                      f"with OpenMP, median of {reps} runs, {sec:.3f} s each"}
 
 
 def run_reference(args):
@@ -255,11 +321,12 @@ def run_reference(args):
     if rank != 0:
         return
     t = time.perf_counter()
-    base = cpu_baseline(reps=max(3, args.steps))
+    n = max(1, args.gpus)  # the job of N GPUs is N sequences per step: time the same N sequences here
+    base = cpu_baseline(reps=max(3, min(args.steps, max(3, 24 // n))), n_seqs=n)
     wall = time.perf_counter() - t
     line = {"impl": "reference", "metric": "gdn_prefill_tokens_per_s", "value": base["value"], "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 * T_PREFILL / base["value"], "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": 1e3 * n * T_PREFILL / base["value"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args.gpus), "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -274,11 +341,22 @@ def workload_config(n):
             "l2": "256 MiB flush write before every timed step; inputs 272 MB > 126 MB L2"}
 
 
-def bench_varlen(args, rank, world):
+def max_tensor_over_ranks(vals, world):
+    t = torch.tensor(vals, dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return [float(x) for x in t.tolist()]
+
+
+def bench_varlen(args, rank, world, steps=None, full_line=True):
     """Packed varlen prefill (64 sequences, log-uniform lengths in [128, 16384], 262144 tokens, nonzero initial
-    states, final states returned), value heads sharded Hv/G per rank, no collective: strong scaling."""
+    states, final states returned), value heads sharded Hv/G per rank, no collective: strong scaling.  Parity
+    (outside the timed region): the shortest, the median and the longest sequence of every rank's heads against
+    the fp64 C checker, worst rank reported."""
     from avelang_b200 import gdn, synth
     from avelang_b200.block import HeadShard
+    from oracle import c_oracle, gdn_oracle
+    steps = steps or args.steps
     inp = synth.config3()
     sh = HeadShard(rank, world, HK, HV)
     ks, vs = slice(sh.key_heads.start, sh.key_heads.stop), slice(sh.value_heads.start, sh.value_heads.stop)
@@ -287,33 +365,67 @@ def bench_varlen(args, rank, world):
     s0, cu = inp.initial_state[:, vs].contiguous().cuda(), inp.cu_seqlens.cuda()
     out = torch.empty_like(v)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
-    longest = max(inp.extras["lengths"])  # the host built the batch, so it knows the longest sequence
-    step = lambda: gdn.chunk_gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=True, cu_seqlens=cu, out=out,
-                                              max_seqlen=longest)
+    lens = inp.extras["lengths"]
+    longest = max(lens)  # the host built the batch, so it knows the longest sequence
+    res = {}
+
+    def step():
+        res["o"], res["s"] = gdn.chunk_gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=True,
+                                                        cu_seqlens=cu, out=out, max_seqlen=longest)
+
     with ClockSampler(torch.cuda.current_device()) as clocks:
-        total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
-    ms = total_ms / args.steps
-    chunks = sum((n + 63) // 64 for n in inp.extras["lengths"])
+        total_ms = max_over_ranks(time_steps(step, steps, args.warmup, world, flush), world)
+    ms = total_ms / steps
+    # parity of this rank's heads
+    order = sorted(range(len(lens)), key=lambda n: lens[n])
+    picks = [order[0], order[len(order) // 2], order[-1]]
+    o_cpu, s_cpu, cul = res["o"].cpu(), res["s"].cpu(), inp.cu_seqlens.tolist()
+    e_o = e_s = 0.0
+    for n in picks:
+        a, b = cul[n], cul[n + 1]
+        o_ref, s_ref = c_oracle.recurrent(inp.q[:, a:b, ks], inp.k[:, a:b, ks], inp.v[:, a:b, vs], inp.g[:, a:b, vs],
+                                          inp.beta[:, a:b, vs], inp.scale, inp.initial_state[n:n + 1, vs])
+        e_o = max(e_o, gdn_oracle.rel_l2(o_cpu[:, a:b].float(), o_ref.to(torch.bfloat16).float()))
+        e_s = max(e_s, gdn_oracle.rel_l2(s_cpu[n:n + 1], s_ref))
+    e_o, e_s, st = max_tensor_over_ranks([e_o, e_s, float(gdn.read_status())], world)
+    parity = {"o_rel_l2_max": e_o, "s_rel_l2_max": e_s, "o_gate": 1e-3, "s_gate": 1e-4, "status_word": int(st),
+              "checked": f"sequences of {[lens[n] for n in picks]} tokens x the heads of every rank, vs the fp64 C checker",
+              "ok": bool(e_o <= 1e-3 and e_s <= 1e-4 and st == 0)}
+    chunks = sum((n + 63) // 64 for n in lens)
     flops = chunks * HV * FLOP_PER_CHUNK_HEAD
+    algo_bytes = 2 * 2 * 262144 * HK * D * 1 + 2 * 2 * 262144 * HV * D + 2 * 4 * 262144 * HV + 2 * 64 * HV * D * D * 4
     peaks = measured_peaks()
     tokens = int(inp.cu_seqlens[-1])
     achieved = flops / (ms * 1e-3) / 1e12
-    return {"metric": "gdn_varlen_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+    line = {"metric": "gdn_varlen_prefill_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16 in / fp32 state and accumulate", "data": "synthetic",
             "config": {"workload": f"varlen packed prefill, 64 seqs, {tokens} tokens, {chunks} chunks, Hk=16, Hv=32, d=128, "
                                    "initial and final states", "parallelism": f"value heads sharded x{world}, no collective",
                        "l2": "256 MiB flush write before every timed step"},
-            "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": gdn.prefill_launch_count(q, k, v, cu_seqlens=cu, max_seqlen=longest) * steps, "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"] * world, "unit": "TFLOP/s",
                          "frac": achieved / (peaks["bf16_tflops"] * world), "traffic": None,
-                         "peak_source": peaks["source"] + " (burst) x n_gpus"}}
+                         "peak_source": peaks["source"] + " (burst) x n_gpus",
+                         "hbm_view": {"achieved_gbs": algo_bytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"] * world,
+                                      "algorithmic_bytes": algo_bytes}},
+            "parity": parity}
+    if not full_line:
+        for key in ("higher_is_better", "vs_baseline", "data", "warmup", "n_gpus", "clocks"):
+            line.pop(key, None)
+    return line
 
 
-def bench_block(args, rank, world):
+def bench_block(args, rank, world, steps=None, full_line=True):
     """Full GDN block, B=4, T=32768, hidden 2048: in-projection, conv1d+SiLU, L2 norm, gate/beta, chunked delta rule,
-    gated RMSNorm on this rank's heads, then the NCCL all-gather of head outputs: strong scaling."""
+    gated RMSNorm on this rank's heads, then the all-gather of head outputs (peer stores fused into the norm kernel;
+    at N >= 2 the NCCL all-gather is timed too and must give the same bits): strong scaling.  Parity (outside the timed
+    region): a causal prefix of one batch row of the gathered output against the CPU block reference, and the
+    delta-rule + norm stage alone against the C checker fed with the device's own stage inputs."""
+    from avelang_b200 import gdn
     from avelang_b200.block import GdnBlockShard
+    from oracle import c_oracle, gdn_oracle
+    steps = steps or args.steps
     B, T, hidden = 4, 32768, 2048
     gen = torch.Generator().manual_seed(0)
     n_out = 2 * HK * D + 2 * HV * D + 2 * HV
@@ -321,27 +433,67 @@ def bench_block(args, rank, world):
     conv_w = (torch.randn(2 * HK * D + HV * D, 4, generator=gen) / 2).bfloat16()
     A_log = torch.rand(HV, generator=gen) * 2.7726
     dt_bias = 0.1 * torch.randn(HV, generator=gen)
-    x = torch.randn(B, T, hidden, generator=gen).bfloat16().cuda()
-    blk = GdnBlockShard(w_in, conv_w, A_log, dt_bias, torch.ones(D), Hk=HK, Hv=HV, dk=D, dv=D, rank=rank, world=world)
+    norm_w = torch.ones(D)
+    x_cpu = torch.randn(B, T, hidden, generator=gen).bfloat16()
+    x = x_cpu.cuda()
+    blk = GdnBlockShard(w_in, conv_w, A_log, dt_bias, norm_w, Hk=HK, Hv=HV, dk=D, dv=D, rank=rank, world=world)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
-    fused = os.environ.get("AVE_GDN_FUSED_GATHER", "1") != "0"  # peer-store all-gather fused into the norm kernel
-    step = lambda: blk.forward(x, fused_gather=fused)
+    fused = os.environ.get("AVE_GDN_FUSED_GATHER", "1") != "0" and world > 1  # peer-store all-gather fused into the norm kernel
+    res = {}
+
+    def step():
+        res["y"] = blk.forward(x, fused_gather=fused)
+
     with ClockSampler(torch.cuda.current_device()) as clocks:
-        total_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world)
-    ms = total_ms / args.steps
+        total_ms = max_over_ranks(time_steps(step, steps, args.warmup, world, flush), world)
+    ms = total_ms / steps
+    y = res["y"]
+    extra = {}
+    if world > 1:  # the same block with one NCCL all-gather instead
+        def step_nccl():
+            res["y_nccl"] = blk.forward(x, fused_gather=False)
+        nccl_ms = max_over_ranks(time_steps(step_nccl, steps, args.warmup, world, flush), world) / steps
+        extra = {"nccl_gather_ms_per_step": nccl_ms, "fused_equals_nccl": bool(torch.equal(y, res["y_nccl"])) if fused else None}
+    # parity 1: causal prefix of batch row 2, every head (they come from every rank), end to end
+    P = 160
+    ref = gdn_oracle.gdn_block_ref(x_cpu[2:3, :P], w_in, conv_w, A_log, dt_bias, norm_w, Hk=HK, Hv=HV, dk=D, dv=D)
+    e_block = gdn_oracle.rel_l2(y[2:3, :P].float().cpu(), ref.bfloat16().float())
+    # parity 2: the delta-rule + norm stage of this rank's heads on the device's own bf16 q/k/v/z and fp32 g/beta
+    keep = {}
+    o_loc = blk.forward_local(x, keep=keep)
+    Pd = 2048
+    cut = lambda t: t[1:2, :Pd].cpu()
+    o_ref, _ = c_oracle.recurrent(cut(keep["q"]), cut(keep["k"]), cut(keep["v"]), cut(keep["g"]), cut(keep["beta"]), D ** -0.5,
+                                  use_qk_l2norm_in_kernel=True)
+    y_ref = gdn_oracle.gated_rmsnorm(o_ref, cut(keep["z"]), norm_w)
+    e_stage = gdn_oracle.rel_l2(o_loc[1:2, :Pd].float().cpu(), y_ref.to(torch.bfloat16).float())
+    e_block, e_stage, st = max_tensor_over_ranks([e_block, e_stage, float(gdn.read_status())], world)
+    parity = {"block_prefix_rel_l2": e_block, "block_gate": 5e-3, "delta_rule_stage_rel_l2_max": e_stage, "stage_gate": 1e-3,
+              "status_word": int(st),
+              "checked": f"{P}-token prefix of batch row 2, all heads, vs the CPU block reference (5e-3: the bf16 projection "
+                         f"and convolution outputs differ from the reference's by a rounding in a few per cent of elements); "
+                         f"delta rule + gated norm on {Pd} tokens of batch row 1, every rank's heads, vs the fp64 C checker "
+                         "fed the device's own stage inputs (1e-3)",
+              "ok": bool(e_block <= 5e-3 and e_stage <= 1e-3 and st == 0 and extra.get("fused_equals_nccl") in (None, True))}
     flops = 2 * B * T * hidden * n_out + (B * T // 64) * HV * FLOP_PER_CHUNK_HEAD
     peaks = measured_peaks()
     achieved = flops / (ms * 1e-3) / 1e12
-    return {"metric": "gdn_block_tokens_per_s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+    line = {"metric": "gdn_block_tokens_per_s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "GDN block B=4 T=32768 hidden 2048: in-proj, conv1d k=4 + SiLU, L2 norm, gate/beta, "
                                    "chunked delta rule, gated RMSNorm, head all-gather",
-                       "parallelism": f"heads sharded x{world}, " + ("all-gather fused into the norm kernel (peer stores)" if fused else "one NCCL all-gather"), "l2": "256 MiB flush write before every timed step"},
-            "gpu_launches": 6 * args.steps, "clocks": clocks.summary(),
+                       "parallelism": f"heads sharded x{world}, " + ("all-gather fused into the norm kernel (peer stores)" if fused else ("one NCCL all-gather" if world > 1 else "no gather")), "l2": "256 MiB flush write before every timed step"},
+            "gpu_launches": (3 + gdn.prefill_launch_count(keep["q"], keep["k"], keep["v"], z=keep["z"], push=fused)) * steps,  # GEMM, conv, gate + the prefill's own
+            "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] * world, "unit": "TFLOP/s",
                          "frac": achieved / (peaks["bf16_tflops_sustained"] * world), "traffic": None,
-                         "peak_source": peaks["source"] + " (sustained) x n_gpus"}}
+                         "peak_source": peaks["source"] + " (sustained) x n_gpus"},
+            "parity": parity, **extra}
+    if not full_line:
+        for key in ("higher_is_better", "vs_baseline", "data", "warmup", "n_gpus", "clocks"):
+            line.pop(key, None)
+    return line
 
 
 def profile_case(name: str):
@@ -377,6 +529,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the varlen and block objects")
     ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block"],
                     help="prefill (default, the headline line), varlen (head-sharded packed prefill) or block")
     ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k"],
@@ -392,6 +545,7 @@ def main():
     from avelang_b200 import _lib
     _lib.load()  # fail loudly when the CUDA library is missing
     rank, world, local = dist_setup(args.gpus)
+    host_binding = bind_host_to_gpu_node(local) if world > 1 else {"numa_node": None, "cpus": None}
     peaks = measured_peaks()
     if args.workload != "prefill":
         line = (bench_varlen if args.workload == "varlen" else bench_block)(args, rank, world)
@@ -401,7 +555,7 @@ def main():
             torch.distributed.destroy_process_group()
         return
 
-    ms, clocks, e2e_ms, h2d, d2h = bench_prefill(args, rank, world)
+    ms, clocks, e2e_ms, h2d, d2h, legs, launches_per_call = bench_prefill(args, rank, world)
     tokens = T_PREFILL * world
     flops = (T_PREFILL // 64) * HV * FLOP_PER_CHUNK_HEAD
     algo_bytes = 272_629_760
@@ -410,8 +564,8 @@ def main():
             "vs_baseline": None, "dtype": "bf16 in / fp32 state and accumulate", "data": "synthetic",
             "config": workload_config(world),
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": 12 * args.steps,  # four chunk ranges (8, 24, 72, 24 chunks) x (prep, scan, gated norm)
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "legs": legs, "host": host_binding},
+            "gpu_launches": launches_per_call * args.steps,  # kernels one prefill call enqueues (asked from the library) x steps
             "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
@@ -437,9 +591,16 @@ def main():
                                        "peak_source": peaks["source"]}}
     if world > 1:
         barrier(world)
+    if rank == 0 and not args.no_cpu and world == 1:
+        line["cpu_baseline"] = cpu_baseline()
+    if not args.no_sharded:
+        # the two sharded workloads over the same ranks, a few steps each, parity checked outside the timed regions
+        sub = max(3, min(args.steps, 10))
+        torch.cuda.empty_cache()
+        line["varlen"] = bench_varlen(args, rank, world, steps=sub, full_line=False)
+        torch.cuda.empty_cache()
+        line["block"] = bench_block(args, rank, world, steps=max(3, min(args.steps, 5)), full_line=False)
     if rank == 0:
-        if not args.no_cpu and world == 1:
-            line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -102,6 +102,9 @@ typedef struct AveGdnArgs {
 /* Chunked prefill (chunk 64, WY/UT form), dense [B,T] or packed varlen via cu_seqlens. */
 int ave_gdn_chunk_prefill(const AveGdnArgs* args, void* stream);
 size_t ave_gdn_prefill_workspace_bytes(const AveGdnArgs* args);
+/* Number of kernels one ave_gdn_chunk_prefill call with these arguments enqueues (a pure function of the shapes and of
+ * which optional tensors are present; no device needed).  0 for invalid arguments. */
+int ave_gdn_prefill_launch_count(const AveGdnArgs* args);
 
 /* Same computation as ave_gdn_chunk_prefill for callers that may not allocate device memory (a serving runtime
  * that has handed all of HBM to its paged pools, a plug-in callback limited to pre-registered buffers, a path where

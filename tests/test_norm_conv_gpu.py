@@ -98,3 +98,12 @@ def test_conv1d_update_matches_full_convolution(gdn, checker):
     # the history now holds the last W-1 inputs, oldest first; untouched slots stay zero
     assert torch.equal(state[4].cpu(), x[0, T - (W - 1):]) and torch.equal(state[0].cpu(), x[2, T - (W - 1):])
     assert torch.count_nonzero(state[1:4]) == 0
+    assert gdn.read_status() == 0  # a negative index is a request to skip, not an error
+    # an index beyond the pool: that sequence is skipped (history and output row untouched) and the status word says so
+    before = state.clone()
+    y_prev = torch.full((N, Cn), 7.0, dtype=torch.bfloat16, device="cuda")
+    bad = torch.tensor([4, 5, 0], dtype=torch.int32, device="cuda")
+    gdn.causal_conv1d_update(x[:, 0].cuda(), state, w.cuda(), state_indices=bad, out=y_prev)
+    assert gdn.read_status() & 1  # AVE_GDN_DEV_BAD_SLOT
+    assert torch.equal(y_prev[1], torch.full((Cn,), 7.0, dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(state[1:4], before[1:4])

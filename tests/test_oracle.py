@@ -100,9 +100,15 @@ def test_golden_small_varlen(checker):
     assert O.rel_l2(O.gated_rmsnorm(o, sm.z), torch.from_numpy(gold["y"])) < 1e-6
 
 
-def test_third_party_opinion(checker):
+def test_third_party_opinion(checker, record_property):
     """Import-only cross-check against an installed third-party package, when present (not the reference)."""
     O, _ = checker
+    import importlib.metadata as md
+    try:
+        version = md.version("flash-linear-attention")
+    except md.PackageNotFoundError:
+        version = "not installed"
+    print(f"third opinion: flash-linear-attention {version}")
     naive = pytest.importorskip("fla.ops.gated_delta_rule.naive", reason="third-party package not installed")
     i = synth.make_inputs(2, 96, 4, 4, 32, 48, seed=3, n_states=2, gate_scale=0.3)
     o1, s1 = O.naive_recurrent_gated_delta_rule(i.q, i.k, i.v, i.g, i.beta, i.scale, i.initial_state)
@@ -110,8 +116,12 @@ def test_third_party_opinion(checker):
         o2, s2 = naive.naive_recurrent_gated_delta_rule(i.q.double(), i.k.double(), i.v.double(), i.beta.double(), i.g.double(),
                                                         scale=i.scale, initial_state=i.initial_state.double(), output_final_state=True)
     except Exception as e:  # signature or layout differs in another version: not our contract
-        pytest.skip(f"third-party call failed: {e!r}")
-    assert O.rel_l2(o2, o1) < 1e-5 and O.rel_l2(s2, s1) < 1e-5
+        print(f"third opinion: call failed in flash-linear-attention {version}: {e!r} -> no opinion given")
+        pytest.skip(f"third-party call failed in flash-linear-attention {version}: {e!r}")
+    e_o, e_s = O.rel_l2(o2, o1), O.rel_l2(s2, s1)
+    print(f"third opinion: flash-linear-attention {version} answered; o rel-L2 {e_o:.2e}, state rel-L2 {e_s:.2e}")
+    record_property("third_opinion", f"flash-linear-attention {version}: o {e_o:.2e}, S {e_s:.2e}")
+    assert e_o < 1e-5 and e_s < 1e-5
 
 
 def test_gated_rmsnorm_properties(checker):
