@@ -296,12 +296,8 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
     if (cis >= per || cis >= plan.part_begin[rest / plan.rn + 1]) return;
     c = (a.cu_seqlens ? chunk_start[n] : n * per) + cis;
   }
-  const ChunkRef cr = find_chunk(a, chunk_start, c);
+  const ChunkRef cr = find_chunk(a, chunk_start, c);  // (a compact grid only ever names chunks of this launch's range)
   if (!cr.ok) return;
-  {
-    const int off = cr.cis - plan.part_begin[part_of(plan, cr.cis)];
-    if (off < plan.r0 || off >= plan.r0 + plan.rn) return;  // not in this launch's range of chunks
-  }
   const int hk = h / (a.Hv / a.Hk);
   const int64_t rec = (int64_t)c * a.Hv + h;
 
@@ -685,6 +681,9 @@ __device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint3
   }
 }
 
+// kMulti: built with the parallel-parts machinery (ScanPlan::parts > 1).  The plain instantiation carries none of its
+// state, which keeps the output warpgroup inside its register budget with 32-token pieces.
+template <bool kMulti>
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, const int32_t* __restrict__ chunk_start,
                      const __nv_bfloat16* __restrict__ w_hi_ws, const __nv_bfloat16* __restrict__ w_lo_ws,
@@ -714,13 +713,13 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // One CTA per (sequence, chain, value head).  Chain 0 is part 0; chains 2p-1 and 2p are the local and the transition
   // chain of part p >= 1 (see ScanPlan).
-  const int chains = 2 * plan.parts - 1;
+  const int chains = kMulti ? 2 * plan.parts - 1 : 1;
   const int h = blockIdx.x % a.Hv;
   const int unit = blockIdx.x / a.Hv;
-  const int chain = unit % chains;
+  const int chain = kMulti ? unit % chains : 0;
   const int n = seq_order ? seq_order[unit / chains] : unit / chains;  // varlen: longest sequences first
   const int part = (chain + 1) >> 1;
-  const bool phi = chain > 0 && (chain & 1) == 0;
+  const bool phi = kMulti && chain > 0 && (chain & 1) == 0;
   const int hk = h / (a.Hv / a.Hk);
   if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;  // the chunk table was rejected: nothing runs
   SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
@@ -745,7 +744,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   }
   const int seq_chunks = (sp.len + C - 1) / C;
   // a sequence that ends inside part 0 is one plain chain: outputs and the final state leave directly
-  const bool multi = plan.parts > 1 && seq_chunks > plan.part_begin[1];
+  const bool multi = kMulti && plan.parts > 1 && seq_chunks > plan.part_begin[1];
   if (chain > 0 && (!multi || plan.part_begin[part] >= seq_chunks)) return;
   int slot = n;
   if (a.state_indices != nullptr) {
@@ -1056,56 +1055,62 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       float* pf = of ? of + tok0 * ((int64_t)a.Hv * D) : nullptr;
       __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
       const int64_t fstep = (int64_t)a.Hv * D, bstep = a.o_stride_t;
+      constexpr int PW = kMulti ? 16 : 32;  // tokens per piece
 #pragma unroll
-      for (int part = 0; part < 4; ++part) {  // 16 tokens at a time: keeps this warpgroup inside its register budget
-        uint32_t o1[16], o2[16];
-        tc::tmem_ld16(lane_addr + TM_O1 + 16 * part, o1);
-        tc::tmem_ld16(lane_addr + TM_O2 + 16 * part, o2);
+      for (int piece = 0; piece < C / PW; ++piece) {
+        uint32_t o1[PW], o2[PW];
+        if constexpr (PW == 16) {
+          tc::tmem_ld16(lane_addr + TM_O1 + PW * piece, o1);
+          tc::tmem_ld16(lane_addr + TM_O2 + PW * piece, o2);
+        } else {
+          tc::tmem_ld32(lane_addr + TM_O1 + PW * piece, o1);
+          tc::tmem_ld32(lane_addr + TM_O2 + PW * piece, o2);
+        }
         tc::tmem_ld_wait();
-        if (part == 3) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
+        if (piece == C / PW - 1) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
           tc::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
         }
-        float ov[16];
+        float ov[PW];
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 qs = *reinterpret_cast<const float4*>(scal + 16 * part + 4 * j4);
+        for (int j4 = 0; j4 < PW / 4; ++j4) {
+          const float4 qs = *reinterpret_cast<const float4*>(scal + PW * piece + 4 * j4);
           const float2 r0 = __ffma2_rn(make_float2(qs.x, qs.y), make_float2(__uint_as_float(o1[4 * j4]), __uint_as_float(o1[4 * j4 + 1])),
                                        make_float2(__uint_as_float(o2[4 * j4]), __uint_as_float(o2[4 * j4 + 1])));
           const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o1[4 * j4 + 3])),
                                        make_float2(__uint_as_float(o2[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 3])));
           ov[4 * j4 + 0] = r0.x; ov[4 * j4 + 1] = r0.y; ov[4 * j4 + 2] = r1.x; ov[4 * j4 + 3] = r1.y;
         }
-        const int n_here = min(16, len - 16 * part);  // tokens of this quarter that exist
+        const int n_here = min(PW, len - PW * piece);  // tokens of this piece that exist
         if (phi) {
           // qt^T of this chunk as bf16 hi and lo images [128 d_k rows][64 tokens] with the 128-byte swizzle: the fix-up
           // reads them, unchanged, as the MN-major A operand of its MMA.  This thread owns row d: two 16-byte pieces.
           uint8_t* img = qt_img + ((int64_t)(c_first + c) * a.Hv + h) * (int64_t)QT_BYTES + d * 128;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
+          for (int e8 = 0; e8 < PW / 8; ++e8) {
             uint32_t hi[4], lo[4];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) split_pair(make_float2(ov[8 * half + 2 * w], ov[8 * half + 2 * w + 1]), hi[w], lo[w]);
-            const uint32_t off = (uint32_t)(((2 * part + half) ^ (d & 7)) << 4);
+            for (int w = 0; w < 4; ++w) split_pair(make_float2(ov[8 * e8 + 2 * w], ov[8 * e8 + 2 * w + 1]), hi[w], lo[w]);
+            const uint32_t off = (uint32_t)((((PW / 8) * piece + e8) ^ (d & 7)) << 4);
             *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
             *reinterpret_cast<uint4*>(img + C * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
           }
         } else if (pf != nullptr) {
-          if (n_here == 16) {
+          if (n_here == PW) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { *pf = ov[j]; pf += fstep; }
+            for (int j = 0; j < PW; ++j) { *pf = ov[j]; pf += fstep; }
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { if (j < n_here) *pf = ov[j]; pf += fstep; }
+            for (int j = 0; j < PW; ++j) { if (j < n_here) *pf = ov[j]; pf += fstep; }
           }
         } else {
-          if (n_here == 16) {
+          if (n_here == PW) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { *pb = __float2bfloat16(ov[j]); pb += bstep; }
+            for (int j = 0; j < PW; ++j) { *pb = __float2bfloat16(ov[j]); pb += bstep; }
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { if (j < n_here) *pb = __float2bfloat16(ov[j]); pb += bstep; }
+            for (int j = 0; j < PW; ++j) { if (j < n_here) *pb = __float2bfloat16(ov[j]); pb += bstep; }
           }
         }
       }
@@ -1626,7 +1631,8 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
   std::lock_guard<std::mutex> guard(dev.mu);
   if (!dev.attr_set) {
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREP_SMEM));
-    AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
+    AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
+    AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
     AVE_CUDA_TRY(cudaFuncSetAttribute(part_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FIN_SMEM));
     dev.attr_set = true;
   }
@@ -1681,8 +1687,8 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     plan.r0 = 0; plan.rn = 1 << 24;  // every chunk (times 64 still fits an int)
     chunk_prep_kernel<<<dim3((unsigned)L.chunks, (unsigned)a.Hv), PREP_THREADS, PREP_SMEM, stream>>>(a, maps, chunk_start, po, plan, 0);
     AVE_CUDA_TRY(cudaGetLastError());
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi,
-                                                                       po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
+    (L.parts > 1 ? chunk_scan_tc_kernel<true> : chunk_scan_tc_kernel<false>)<<<scan_grid, SCAN_THREADS, SCAN_SMEM, stream>>>(
+        a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
     AVE_CUDA_TRY(cudaGetLastError());
     if (a.z != nullptr) {
       // packed layouts: the norm covers every row (rows of later parts are rewritten by the fix-up, which runs after it)
@@ -1711,8 +1717,8 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     if (!step(cudaGetLastError())) break;
     if (!step(cudaEventRecord(side->done[i], side->prep))) break;
     if (!step(cudaStreamWaitEvent(side->scan, side->done[i], 0))) break;
-    chunk_scan_tc_kernel<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo,
-                                                                           po.tu_hi, po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
+    (L.parts > 1 ? chunk_scan_tc_kernel<true> : chunk_scan_tc_kernel<false>)<<<scan_grid, SCAN_THREADS, SCAN_SMEM, side->scan>>>(
+        a, maps, chunk_start, po.w_hi, po.w_lo, po.p_hi, po.p_lo, po.tu_hi, po.tu_lo, po.scal, o_f32, qt_img, carry, m0_pack, seq_order, plan);
     if (!step(cudaGetLastError())) break;
     if (norm_per_range) {
       if (!step(cudaEventRecord(side->scanned[i], side->scan))) break;
