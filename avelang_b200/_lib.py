@@ -53,6 +53,14 @@ class ConvUpdateArgs(ctypes.Structure):
                 ("x_stride", I64), ("y_stride", I64), ("status", P)]
 
 
+class DecodeLayerArgs(ctypes.Structure):
+    _fields_ = ([("struct_size", U32), ("flags", U32)]
+                + [(n, P) for n in ("proj", "conv_w", "conv_bias", "conv_state", "A_log", "dt_bias", "norm_weight", "state_pool",
+                                    "state_indices", "o", "status")]
+                + [(n, I32) for n in ("n_seqs", "Hk", "Hv", "dk", "dv", "width", "num_slots", "reserved0")]
+                + [("proj_stride", I64), ("o_stride", I64), ("scale", F32), ("norm_eps", F32)])
+
+
 class GateArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("A_log", P), ("dt_bias", P),
                 ("g", P), ("beta", P), ("rows", I64), ("Hv", I32), ("reserved0", I32),
@@ -71,6 +79,7 @@ SYMBOLS = {
     "ave_gdn_conv1d_silu": (ctypes.c_int, [ctypes.POINTER(ConvArgs), P]),
     "ave_gdn_conv1d_update": (ctypes.c_int, [ctypes.POINTER(ConvUpdateArgs), P]),
     "ave_gdn_gate_beta": (ctypes.c_int, [ctypes.POINTER(GateArgs), P]),
+    "ave_gdn_decode_layer_step": (ctypes.c_int, [ctypes.POINTER(DecodeLayerArgs), P]),
     "ave_gdn_abi_version": (ctypes.c_int, []),
     "ave_gdn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ave_gdn_last_cuda_error": (ctypes.c_int, []),

@@ -16,6 +16,7 @@ int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
 int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
+int launch_decode_layer(const AveGdnDecodeLayerArgs& a, cudaStream_t stream);
 
 static size_t prefill_ws_bytes(const AveGdnArgs& a) {
   return a.dk == 128 ? prefill_tc_workspace_bytes(a, false) : prefill_simt_workspace_bytes(a);
@@ -137,6 +138,21 @@ int ave_gdn_conv1d_update(const AveConvUpdateArgs* a, void* stream) {
   if (a->state_indices == nullptr && a->num_slots < a->n_seqs) return AVE_GDN_INVALID_ARGUMENT;
   if (!aligned16(a->x) || !aligned16(a->y) || !aligned16(a->conv_state) || (a->x_stride % 8) || (a->y_stride % 8)) return AVE_GDN_MISALIGNED;
   return launch_conv1d_update(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ave_gdn_decode_layer_step(const AveGdnDecodeLayerArgs* a, void* stream) {
+  if (a == nullptr || a->struct_size != sizeof(AveGdnDecodeLayerArgs)) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->n_seqs < 0 || a->Hk <= 0 || a->Hv <= 0 || a->num_slots < 0 || a->Hv % a->Hk != 0) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->dk != 128 || a->dv != 128 || a->width < 2 || a->width > 4) return AVE_GDN_UNSUPPORTED;
+  if (a->n_seqs == 0) return AVE_GDN_OK;
+  if (!a->proj || !a->conv_w || !a->conv_state || !a->A_log || !a->dt_bias || !a->state_pool || !a->o) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->state_indices == nullptr && a->num_slots < a->n_seqs) return AVE_GDN_INVALID_ARGUMENT;
+  const int64_t cols = 2 * (int64_t)a->Hk * a->dk + 2 * (int64_t)a->Hv * a->dv + 2 * a->Hv;
+  if (a->proj_stride < cols || a->o_stride < (int64_t)a->Hv * a->dv) return AVE_GDN_INVALID_ARGUMENT;
+  if (!aligned16(a->proj) || !aligned16(a->o) || !aligned16(a->state_pool) || !aligned16(a->conv_state) || (a->proj_stride % 8) ||
+      (a->o_stride % 8))
+    return AVE_GDN_MISALIGNED;
+  return launch_decode_layer(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ave_gdn_gate_beta(const AveGateArgs* a, void* stream) {

@@ -73,9 +73,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   producer_done:;
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::idesc_f16(BM, BN, 1, 1, false, false);
       int s = 0; uint32_t ph = 0; int local = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+        // a ragged last column tile issues MMAs only as wide as the columns that exist (N of the instruction in steps of
+        // 16): with N = 1544 the seventh tile is 8 columns wide and costs a sixteenth of a full one on the tensor pipe
+        const int64_t n_left = N - (int64_t)tile_coord(tile, mt, nt).n * BN;
+        const int n_mma = n_left >= BN ? BN : (int)((n_left + 15) / 16) * 16;
+        const uint32_t idesc = tc::idesc_f16(BM, n_mma, 1, 1, false, false);
         const int buf = local & 1;
         const uint32_t acc_ph = (uint32_t)(local >> 1) & 1u;
         if (!tc::mbar_wait(&acc_empty[buf], acc_ph ^ 1u, abort_flag)) break;
@@ -111,8 +115,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int64_t row = (int64_t)tcd.m * BM + quarter * 32 + lane;
       __nv_bfloat16* crow = C + row * ldc + (int64_t)tcd.n * BN;
       const int64_t n_left = N - (int64_t)tcd.n * BN;
+      const int col_groups = n_left >= BN ? BN / 32 : (int)((n_left + 31) / 32);  // 32-column groups that hold results
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < col_groups; ++c) {
         uint32_t r[32];
         tc::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
         tc::tmem_ld_wait();

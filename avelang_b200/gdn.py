@@ -24,7 +24,7 @@ import torch
 from . import _lib, torch_ops
 
 __all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "mixed_prefill_decode_step", "gated_rmsnorm",
-           "causal_conv1d_silu", "causal_conv1d_update", "gate_beta", "prefill_launch_count", "read_status"]
+           "causal_conv1d_silu", "causal_conv1d_update", "gate_beta", "decode_layer_step", "prefill_launch_count", "read_status"]
 
 _status_words: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -309,6 +309,72 @@ def mixed_prefill_decode_step(q, k, v, g, beta, cu_seqlens, n_decode, state_pool
                                norm_weight=norm_weight, norm_eps=norm_eps, state_indices=state_indices[nd:].contiguous(),
                                out=rest(o))
     return o
+
+
+def decode_layer_step(proj, conv_weight, conv_state, A_log, dt_bias, state_pool, state_indices=None, *, Hk, Hv, conv_bias=None,
+                      norm_weight=None, norm_eps=1e-6, scale=None, gate_first=False, out=None):
+    """One decode step of a whole GDN layer behind its in-projection, in one kernel.  ``proj``: bf16 ``[N, >= 2*Hk*128 +
+    2*Hv*128 + 2*Hv]``, each row the new token's projection ``[q | k | v | z | b | a]`` (a column slice of a wider matrix
+    is accepted); ``conv_weight`` bf16 ``[2*Hk*128 + Hv*128, W]`` (W in 2..4, rows in q | k | v order), ``conv_state`` bf16
+    ``[slots, W-1, C]`` and ``state_pool`` fp32 ``[slots, Hv, 128, 128]`` share the slot index ``state_indices[n]`` (or n)
+    and are updated in place; ``A_log``, ``dt_bias`` ``[Hv]``.  Computes conv update + SiLU, q/k L2 norm, gate and beta,
+    the delta-rule update and the gated RMSNorm with z; the results are those of ``causal_conv1d_update`` + ``gate_beta`` +
+    ``fused_recurrent_gated_delta_rule`` run one after the other.  Returns ``o [N, Hv, 128]``."""
+    d = 128
+    _req(proj.dtype == torch.bfloat16 and proj.dim() == 2 and proj.is_cuda and proj.stride(1) == 1, "proj must be a bf16 CUDA tensor [N, columns]")
+    N = proj.shape[0]
+    _req(Hk > 0 and Hv > 0 and Hv % Hk == 0, f"value heads ({Hv}) must be a multiple of key heads ({Hk}).")
+    Cn, cols = 2 * Hk * d + Hv * d, 2 * Hk * d + 2 * Hv * d + 2 * Hv
+    _req(proj.shape[1] >= cols, f"proj must have at least {cols} columns, got {proj.shape[1]}.")
+    _req(conv_weight.dtype == torch.bfloat16 and conv_weight.dim() == 2 and conv_weight.shape[0] == Cn and 2 <= conv_weight.shape[1] <= 4
+         and conv_weight.device == proj.device, f"conv_weight must be a bf16 tensor [{Cn}, W] with W in 2..4 on {proj.device}")
+    W = conv_weight.shape[1]
+    _req(conv_state.dtype == torch.bfloat16 and conv_state.dim() == 3 and tuple(conv_state.shape[1:]) == (W - 1, Cn)
+         and conv_state.is_contiguous() and conv_state.device == proj.device,
+         f"conv_state must be a contiguous bf16 tensor [slots, {W - 1}, {Cn}] on {proj.device}")
+    _req(state_pool.dtype == torch.float32 and state_pool.dim() == 4 and tuple(state_pool.shape[1:]) == (Hv, d, d)
+         and state_pool.is_contiguous() and state_pool.device == proj.device,
+         f"state_pool must be a contiguous fp32 tensor [slots, {Hv}, {d}, {d}] on {proj.device}")
+    _req(state_pool.shape[0] == conv_state.shape[0], "conv_state and state_pool must have the same number of slots")
+    if state_indices is not None:
+        _req(state_indices.dtype == torch.int32 and tuple(state_indices.shape) == (N,) and state_indices.device == proj.device
+             and state_indices.is_contiguous(), f"state_indices must be a contiguous int32 tensor ({N},) on {proj.device}")
+    else:
+        _req(state_pool.shape[0] >= N, "the pools need one slot per sequence when state_indices is not given")
+    A_log, dt_bias = A_log.detach().float().contiguous(), dt_bias.detach().float().contiguous()
+    _req(A_log.numel() == Hv and dt_bias.numel() == Hv and A_log.device == proj.device, f"A_log and dt_bias must have {Hv} elements on {proj.device}")
+    if norm_weight is not None:
+        _req(norm_weight.numel() == d and norm_weight.device == proj.device, f"norm_weight must have {d} elements on {proj.device}")
+        norm_weight = norm_weight.detach().float().contiguous()
+    if conv_bias is not None:
+        _req(conv_bias.dtype == torch.bfloat16 and conv_bias.numel() == Cn and conv_bias.device == proj.device, f"conv_bias must be bf16 [{Cn}]")
+        conv_bias = conv_bias.contiguous()
+    if out is None:
+        out = torch.empty((N, Hv, d), dtype=torch.bfloat16, device=proj.device)
+    _req(tuple(out.shape) == (N, Hv, d) and out.dtype == torch.bfloat16 and out.device == proj.device and out.stride(2) == 1
+         and out.stride(1) == d, f"out must be a bf16 tensor ({N}, {Hv}, {d}) with contiguous rows on {proj.device}")
+    torch_ops.op("decode_layer_step")(proj, conv_weight.contiguous(), conv_bias, conv_state, A_log, dt_bias, norm_weight, state_pool,
+                                      state_indices, out, int(Hk), int(Hv), float(d ** -0.5 if scale is None else scale), float(norm_eps),
+                                      bool(gate_first))
+    return out
+
+
+@torch_ops.implement("decode_layer_step")
+def _decode_layer_step(proj, conv_w, conv_bias, conv_state, A_log, dt_bias, norm_weight, state_pool, state_indices, out, Hk, Hv,
+                       scale, norm_eps, gate_first):
+    """torch.ops.avelang_gdn.decode_layer_step -> ave_gdn_decode_layer_step on the current stream."""
+    a = _lib.DecodeLayerArgs()
+    a.struct_size = ctypes.sizeof(_lib.DecodeLayerArgs)
+    a.flags = _lib.FLAG_GATE_FIRST if gate_first else 0
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    a.proj, a.conv_w, a.conv_bias, a.conv_state = ptr(proj), ptr(conv_w), ptr(conv_bias), ptr(conv_state)
+    a.A_log, a.dt_bias, a.norm_weight, a.state_pool = ptr(A_log), ptr(dt_bias), ptr(norm_weight), ptr(state_pool)
+    a.state_indices, a.o, a.status = ptr(state_indices), ptr(out), _status_word(proj.device).data_ptr()
+    a.n_seqs, a.Hk, a.Hv, a.dk, a.dv, a.width, a.num_slots = proj.shape[0], Hk, Hv, 128, 128, conv_w.shape[1], state_pool.shape[0]
+    a.proj_stride, a.o_stride, a.scale, a.norm_eps = proj.stride(0), out.stride(0), scale, norm_eps
+    with torch.cuda.device(proj.device):
+        rc = _lib.load().ave_gdn_decode_layer_step(ctypes.byref(a), torch.cuda.current_stream(proj.device).cuda_stream)
+    _lib.check(rc, "decode_layer_step")
 
 
 def gated_rmsnorm(x, z, weight=None, eps=1e-6, *, gate_first=False, out=None):

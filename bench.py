@@ -496,6 +496,68 @@ def bench_block(args, rank, world, steps=None, full_line=True):
     return line
 
 
+def bench_helpers(args):
+    """The kernels around the recurrence, each timed alone on one GPU (CUDA events, L2 flush between runs): the bf16
+    GEMM on the in-projection shapes next to torch.matmul (cuBLAS) in the same run, the causal conv1d + SiLU, the
+    fp32-input gated norm and the gate/beta kernel, with the bytes or flops each moves."""
+    from avelang_b200 import gdn, gemm
+    torch.cuda.set_device(0)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    peaks = measured_peaks()
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            flush.add_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    out = {"metric": "gdn_helper_kernels", "peaks": peaks, "gemm": [], "streaming": []}
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    for (m, n, k, what) in ((131072, 1544, 2048, "in-projection of one rank of eight"), (131072, 12352, 2048, "in-projection, one GPU"),
+                            (8192, 8192, 8192, "square")):
+        A = torch.randn(m, k, device="cuda", generator=gen).bfloat16()
+        B = (0.02 * torch.randn(n, k, device="cuda", generator=gen)).bfloat16()
+        C = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        ours = timed(lambda: gemm.gemm_pipeline_transposed_b(A, B, out=C))
+        ref = timed(lambda: torch.matmul(A, B.T, out=C))
+        fl = 2.0 * m * n * k
+        out["gemm"].append({"shape": [m, n, k], "what": what, "ms": ours, "tflops": fl / ours / 1e9, "cublas_ms": ref,
+                            "cublas_tflops": fl / ref / 1e9, "frac_of_cublas": ref / ours,
+                            "frac_of_measured_peak": fl / ours / 1e9 / peaks["bf16_tflops_sustained"]})
+        del A, B, C
+    Bt, T, Cn = 4, 32768, 8192
+    x = torch.randn(Bt, T, Cn, device="cuda", generator=gen).bfloat16()
+    w = (torch.randn(Cn, 4, device="cuda", generator=gen) / 2).bfloat16()
+    y = torch.empty_like(x)
+    ms = timed(lambda: gdn.causal_conv1d_silu(x, w, out=y))
+    by = 2 * x.numel() * 2
+    out["streaming"].append({"kernel": "conv1d_silu_kernel<4>", "shape": [Bt, T, Cn], "ms": ms, "GBps": by / ms / 1e6,
+                             "frac_of_measured_hbm": by / ms / 1e6 / peaks["hbm_gbs"], "bytes": by})
+    del x, y
+    rows, H = Bt * T, 32
+    xo = torch.randn(rows, H, 128, device="cuda", generator=gen).bfloat16()
+    z = torch.randn(rows, H, 128, device="cuda", generator=gen).bfloat16()
+    yo = torch.empty_like(xo)
+    ms = timed(lambda: gdn.gated_rmsnorm(xo, z, out=yo))
+    by = 3 * xo.numel() * 2
+    out["streaming"].append({"kernel": "gated_rmsnorm_kernel<128, bf16>", "shape": [rows, H, 128], "ms": ms, "GBps": by / ms / 1e6,
+                             "frac_of_measured_hbm": by / ms / 1e6 / peaks["hbm_gbs"], "bytes": by})
+    a_in = torch.randn(rows, H, device="cuda", generator=gen).bfloat16()
+    b_in = torch.randn(rows, H, device="cuda", generator=gen).bfloat16()
+    A_log, dt = torch.rand(H, device="cuda"), torch.randn(H, device="cuda") * 0.1
+    ms = timed(lambda: gdn.gate_beta(a_in, b_in, A_log, dt))
+    by = rows * H * (2 + 2 + 4 + 4)
+    out["streaming"].append({"kernel": "gate_beta_kernel", "shape": [rows, H], "ms": ms, "GBps": by / ms / 1e6,
+                             "frac_of_measured_hbm": by / ms / 1e6 / peaks["hbm_gbs"], "bytes": by})
+    print(json.dumps(out))
+
+
 def profile_case(name: str):
     """Small fixed cases for profiler captures (a few launches, a few hundred MB on the device at most)."""
     from avelang_b200 import gdn, synth
@@ -515,6 +577,18 @@ def profile_case(name: str):
         for _ in range(2):
             gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, initial_state=inp.initial_state,
                                        output_final_state=True, cu_seqlens=inp.cu_seqlens)
+    elif name == "gemm1544":
+        # the in-projection of one rank of eight at an eighth of the rows (16384 x 1544 x 2048): ragged last column tile
+        from avelang_b200 import gemm
+        A = torch.randn(16384, 2048, device="cuda").bfloat16()
+        B = (0.02 * torch.randn(1544, 2048, device="cuda")).bfloat16()
+        for _ in range(3):
+            gemm.gemm_pipeline_transposed_b(A, B)
+    elif name == "conv":
+        x = torch.randn(1, 32768, 8192, device="cuda").bfloat16()  # 512 MiB in, 512 MiB out
+        w = (torch.randn(8192, 4, device="cuda") / 2).bfloat16()
+        for _ in range(3):
+            gdn.causal_conv1d_silu(x, w)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     torch.cuda.synchronize()
@@ -530,9 +604,10 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sharded", action="store_true", help="skip the varlen and block objects")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block"],
-                    help="prefill (default, the headline line), varlen (head-sharded packed prefill) or block")
-    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k"],
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block", "helpers"],
+                    help="prefill (default, the headline line), varlen (head-sharded packed prefill), block, or helpers "
+                         "(GEMM, conv1d, norm and gate kernels timed alone on one GPU)")
+    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k", "gemm1544", "conv"],
                     help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
     if args.profile_case:
@@ -544,6 +619,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
     from avelang_b200 import _lib
     _lib.load()  # fail loudly when the CUDA library is missing
+    if args.workload == "helpers":
+        return bench_helpers(args)
     rank, world, local = dist_setup(args.gpus)
     host_binding = bind_host_to_gpu_node(local) if world > 1 else {"numa_node": None, "cpus": None}
     peaks = measured_peaks()

@@ -188,6 +188,34 @@ typedef struct AveConvUpdateArgs {
 } AveConvUpdateArgs;
 int ave_gdn_conv1d_update(const AveConvUpdateArgs* args, void* stream);
 
+/* One decode step of a whole GDN layer behind its in-projection, fused into one kernel: per sequence n the new token's
+ * projection row proj[n] = [q | k | v | z | b | a] (Hk*dk | Hk*dk | Hv*dv | Hv*dv | Hv | Hv columns, bf16) goes through
+ * the causal-conv update + SiLU on the q, k, v channels (history of slot state_indices[n] of conv_state shifted in
+ * place), the L2 norm of q and k per head (eps 1e-6), g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b), the
+ * gated-delta-rule update of the fp32 state tiles of that slot of state_pool (in place) and the gated RMSNorm with z.
+ * Same rounding points as ave_gdn_conv1d_update + ave_gdn_gate_beta + ave_gdn_decode_step run one after the other.
+ * dk = dv = 128.  Negative slot: the sequence is skipped (o = 0, no state access); slot >= num_slots: skipped and
+ * flagged AVE_GDN_DEV_BAD_SLOT.  The two pools share the slot index. */
+typedef struct AveGdnDecodeLayerArgs {
+  uint32_t struct_size;
+  uint32_t flags;               /* AVE_GDN_FLAG_GATE_FIRST */
+  const void* proj;             /* bf16 [n_seqs, proj_stride] */
+  const void* conv_w;           /* bf16 [2*Hk*dk + Hv*dv, width], rows in q | k | v channel order */
+  const void* conv_bias;        /* bf16 [2*Hk*dk + Hv*dv], optional */
+  void* conv_state;             /* bf16 [num_slots, width-1, 2*Hk*dk + Hv*dv], oldest first */
+  const float* A_log;           /* fp32 [Hv] */
+  const float* dt_bias;         /* fp32 [Hv] */
+  const float* norm_weight;     /* fp32 [dv], optional */
+  float* state_pool;            /* fp32 [num_slots, Hv, dk, dv] */
+  const int32_t* state_indices; /* optional int32 [n_seqs] */
+  void* o;                      /* bf16 [n_seqs, o_stride]: Hv*dv normalised outputs per sequence */
+  uint32_t* status;             /* optional device status word */
+  int32_t n_seqs, Hk, Hv, dk, dv, width, num_slots, reserved0;
+  int64_t proj_stride, o_stride; /* row strides in elements, multiples of 8 */
+  float scale, norm_eps;
+} AveGdnDecodeLayerArgs;
+int ave_gdn_decode_layer_step(const AveGdnDecodeLayerArgs* args, void* stream);
+
 /* g = -exp(A_log[h]) * softplus(a + dt_bias[h]),  beta = sigmoid(b);  a,b bf16 [rows,Hv] (strided),
  * A_log,dt_bias fp32 [Hv];  g,beta fp32 [rows,Hv] contiguous. */
 typedef struct AveGateArgs {

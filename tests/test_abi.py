@@ -31,15 +31,17 @@ def test_exports_every_declared_symbol(built_lib):
 
 def test_struct_mirrors_match_header(tmp_path):
     src = tmp_path / "sz.c"
-    src.write_text('#include "ave_gdn.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include "ave_gdn.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(AveGdnArgs),sizeof(AveGdnNormArgs),sizeof(AveGemmArgs),sizeof(AveConvArgs),sizeof(AveGateArgs),"
-                   "offsetof(AveGdnArgs,scale),offsetof(AveGdnArgs,q_stride_b));return 0;}\n")
+                   "offsetof(AveGdnArgs,scale),offsetof(AveGdnArgs,q_stride_b),sizeof(AveConvUpdateArgs),sizeof(AveGdnDecodeLayerArgs),"
+                   "offsetof(AveGdnDecodeLayerArgs,proj_stride),offsetof(AveGemmArgs,status));return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     want = [ctypes.sizeof(_lib.GdnArgs), ctypes.sizeof(_lib.NormArgs), ctypes.sizeof(_lib.GemmArgs),
             ctypes.sizeof(_lib.ConvArgs), ctypes.sizeof(_lib.GateArgs), _lib.GdnArgs.scale.offset,
-            _lib.GdnArgs.q_stride_b.offset]
+            _lib.GdnArgs.q_stride_b.offset, ctypes.sizeof(_lib.ConvUpdateArgs), ctypes.sizeof(_lib.DecodeLayerArgs),
+            _lib.DecodeLayerArgs.proj_stride.offset, _lib.GemmArgs.status.offset]
     assert got == want
 
 

@@ -136,3 +136,68 @@ def test_prefill_into_pool_then_decode_matches_recurrence(gdn, checker):
     check_o(O, o_p.reshape(N, Tp, Hv, d), o_ref[:, :Tp])
     check_o(O, torch.cat(outs, 1), o_ref[:, Tp:])
     check_s(O, pool[idx.long()], s_ref)
+
+
+def test_decode_layer_step_matches_separate_kernels_and_checker(gdn, checker):
+    """The fused decode step of a whole layer (conv update + SiLU, q/k L2 norm, gate/beta, delta-rule update, gated norm
+    in one kernel) over three chained steps with shared slot pools: bit-identical to the separate kernels run one after
+    the other (same rounding points), and within the parity gates of the fp64 checker's composition."""
+    O, C = checker
+    N, Hk, Hv, d, W, slots = 6, 2, 4, 128, 4, 9
+    Cn, cols = 2 * Hk * d + Hv * d, 2 * Hk * d + 2 * Hv * d + 2 * Hv
+    gen = torch.Generator().manual_seed(17)
+    conv_w = (torch.randn(Cn, W, generator=gen) / 2).bfloat16()
+    A_log, dt_bias = torch.rand(Hv, generator=gen) * 2.77, 0.1 * torch.randn(Hv, generator=gen)
+    norm_w = 1.0 + 0.1 * torch.randn(d, generator=gen)
+    idx = torch.tensor([3, -1, 0, 7, 5, 8], dtype=torch.int32)
+    pool0 = 0.02 * torch.randn(slots, Hv, d, d, generator=gen)
+    conv0 = torch.randn(slots, W - 1, Cn, generator=gen).bfloat16()
+    pool_f, pool_s, conv_f, conv_s = pool0.cuda(), pool0.cuda(), conv0.cuda(), conv0.cuda()
+    pool_ref, conv_ref = pool0.double(), conv0.double()
+    cw, Al, dtb, nw, ix = conv_w.cuda(), A_log.cuda(), dt_bias.cuda(), norm_w.cuda(), idx.cuda()
+    for step in range(3):
+        proj = torch.randn(N, cols + 8, generator=gen)
+        proj[:, cols - 2 * Hv:cols] *= 2.0  # b and a drive sigmoid and softplus: give them range
+        proj = proj.bfloat16()
+        pg = proj.cuda()[:, :cols]  # a column slice of a wider projection output
+        o_f = gdn.decode_layer_step(pg, cw, conv_f, Al, dtb, pool_f, ix, Hk=Hk, Hv=Hv, norm_weight=nw)
+        # the same step from the separate entry points
+        qkv = gdn.causal_conv1d_update(pg[:, :Cn], conv_s, cw, state_indices=ix)
+        q = qkv[:, :Hk * d].reshape(N, 1, Hk, d)
+        k = qkv[:, Hk * d:2 * Hk * d].reshape(N, 1, Hk, d)
+        v = qkv[:, 2 * Hk * d:].reshape(N, 1, Hv, d)
+        z = pg[:, Cn:Cn + Hv * d].reshape(N, 1, Hv, d)
+        g, beta = gdn.gate_beta(pg[:, cols - Hv:cols], pg[:, cols - 2 * Hv:cols - Hv], Al, dtb)
+        o_s, _ = gdn.fused_recurrent_gated_delta_rule(q, k, v, g.reshape(N, 1, Hv), beta.reshape(N, 1, Hv), initial_state=pool_s,
+                                                      state_indices=ix, use_qk_l2norm_in_kernel=True, z=z, norm_weight=nw)
+        assert gdn.read_status() == 0
+        assert torch.equal(o_f, o_s.reshape(N, Hv, d)) and torch.equal(pool_f, pool_s) and torch.equal(conv_f, conv_s)
+        assert torch.count_nonzero(o_f[1]) == 0
+        # the checker's composition, sequence by sequence
+        for n in range(N):
+            sl = int(idx[n])
+            if sl < 0:
+                continue
+            x = proj[n:n + 1, :cols].double()
+            hist = torch.cat([conv_ref[sl], x[:, :Cn]], 0)[None]                    # [1, W, Cn]
+            y = O.causal_conv1d_silu(hist, conv_w)[:, -1].to(torch.bfloat16).double()  # rounded where the device rounds
+            conv_ref[sl] = hist[0, 1:]
+            qr = O.l2norm(y[:, :Hk * d].reshape(1, 1, Hk, d))
+            kr = O.l2norm(y[:, Hk * d:2 * Hk * d].reshape(1, 1, Hk, d))
+            vr = y[:, 2 * Hk * d:].reshape(1, 1, Hv, d)
+            zr = x[:, Cn:Cn + Hv * d].reshape(1, 1, Hv, d)
+            gr, br = O.gate_beta(x[:, cols - Hv:cols], x[:, cols - 2 * Hv:cols - Hv], A_log, dt_bias)
+            o_r, s_r = O.naive_recurrent_gated_delta_rule(qr, kr, vr, gr.float().double().reshape(1, 1, Hv), br.float().double().reshape(1, 1, Hv),
+                                                          d ** -0.5, pool_ref[sl:sl + 1])
+            pool_ref[sl] = s_r[0]
+            y_r = O.gated_rmsnorm(o_r, zr, norm_w)
+            assert O.rel_l2(o_f[n].float().cpu(), y_r[0, 0].to(torch.bfloat16).float()) <= 1e-3, (step, n)
+            assert O.rel_l2(pool_f[sl].cpu(), s_r[0]) <= 1e-4, (step, n)
+    assert torch.equal(conv_f.cpu().double(), conv_ref)
+    # an index beyond the pools: skipped and flagged
+    bad = torch.tensor([3, 99, 0, 7, 5, 8], dtype=torch.int32, device="cuda")
+    before = pool_f.clone()
+    o_b = gdn.decode_layer_step(pg, cw, conv_f, Al, dtb, pool_f, bad, Hk=Hk, Hv=Hv, norm_weight=nw)
+    assert gdn.read_status() & 1 and torch.count_nonzero(o_b[1]) == 0
+    untouched = [s for s in range(slots) if s not in (3, 0, 7, 5, 8)]
+    assert torch.equal(pool_f[untouched], before[untouched])
