@@ -10,7 +10,7 @@
 // a time and walks the value heads that share it back to back: q and k are convolved and their history shifted once,
 // by the one CTA that reads them, which is what makes the in-place history update free of races.
 // Rounding points are those of the separate kernels (convolution outputs are rounded to bf16, g and beta stay fp32), so
-// the fused step gives the bits of conv1d_update + gate_beta + decode_step.
+// the fused step leaves the states and histories that conv1d_update + gate_beta + decode_step leave, bit for bit.
 #include "common.cuh"
 #include "tc.cuh"
 
