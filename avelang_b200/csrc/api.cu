@@ -113,9 +113,10 @@ int ave_gdn_gated_rmsnorm(const AveGdnNormArgs* a, void* stream) {
   if (a->rows == 0) return AVE_GDN_OK;
   if (!a->x || !a->z || !a->y) return AVE_GDN_INVALID_ARGUMENT;
   const int64_t strides[] = {a->x_stride_t, a->x_stride_h, a->z_stride_t, a->z_stride_h, a->y_stride_t, a->y_stride_h};
+  const int64_t need = a->d == 128 ? 16 : 8;  // bytes a lane loads at once
   for (int64_t s : strides)
-    if ((s * 2) % 8) return AVE_GDN_MISALIGNED;
-  if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->z) | reinterpret_cast<uintptr_t>(a->y)) & 7u) return AVE_GDN_MISALIGNED;
+    if ((s * 2) % need) return AVE_GDN_MISALIGNED;
+  if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->z) | reinterpret_cast<uintptr_t>(a->y)) & (uintptr_t)(need - 1)) return AVE_GDN_MISALIGNED;
   return launch_gated_rmsnorm(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -46,6 +46,24 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// silu of two values with the multiplies and the add as packed fp32 pairs (one instruction per pair); the exponential
+// and the reciprocal stay scalar special-function operations
+__device__ __forceinline__ float2 silu2(float2 x) {
+  const float2 t = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(t.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(t.y));
+  const float2 d = __ffma2_rn(e, make_float2(1.f, 1.f), make_float2(1.f, 1.f));
+  float2 r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(d.y));
+  return __fmul2_rn(x, r);
+}
+// two bf16 values packed in 32 bits -> fp32 pair (a 16-bit shift and a mask)
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t raw) {
+  return make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
+}
+
 // Sequence n of a dense [B,T] batch or of a packed varlen batch: batch row, first token, length.
 struct SeqSpan {
   int b;

@@ -5,8 +5,10 @@ namespace ave {
 
 // One thread owns 8 adjacent channels (one 16-byte load per token) and walks a run of tokens with the
 // last width-1 inputs held in registers, so each input element is read from HBM once per run (+ halo).
+// The kernel is bound by instruction issue, not by HBM (about 6 bytes cross the memory system per warp instruction
+// the SMs can issue), so the arithmetic runs on packed fp32 pairs: one FFMA2 per tap and channel pair.
 template <int WIDTH>
-__global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, int tokens_per_cta) {
+__global__ void __launch_bounds__(128) conv1d_silu_kernel(const AveConvArgs a, int tokens_per_cta) {
   const int cg = blockIdx.x * blockDim.x + threadIdx.x;  // channel group
   if (cg * 8 >= a.C) return;
   const int b = blockIdx.z;
@@ -16,14 +18,16 @@ __global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, i
   const __nv_bfloat16* xg = reinterpret_cast<const __nv_bfloat16*>(a.x) + b * a.x_stride_b + cg * 8;
   __nv_bfloat16* yg = reinterpret_cast<__nv_bfloat16*>(a.y) + b * a.y_stride_b + cg * 8;
 
-  float w[8][WIDTH], bias[8];
+  float2 w[4][WIDTH], bias[4];  // channel pairs
   {
     const __nv_bfloat16* wg = reinterpret_cast<const __nv_bfloat16*>(a.w) + (int64_t)cg * 8 * WIDTH;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
 #pragma unroll
-      for (int j = 0; j < WIDTH; ++j) w[c][j] = bf2f(wg[c * WIDTH + j]);
-      bias[c] = a.bias ? bf2f(reinterpret_cast<const __nv_bfloat16*>(a.bias)[cg * 8 + c]) : 0.f;
+      for (int j = 0; j < WIDTH; ++j) w[c][j] = make_float2(bf2f(wg[(2 * c) * WIDTH + j]), bf2f(wg[(2 * c + 1) * WIDTH + j]));
+      bias[c] = a.bias ? make_float2(bf2f(reinterpret_cast<const __nv_bfloat16*>(a.bias)[cg * 8 + 2 * c]),
+                                     bf2f(reinterpret_cast<const __nv_bfloat16*>(a.bias)[cg * 8 + 2 * c + 1]))
+                       : make_float2(0.f, 0.f);
     }
   }
   // sequence containing t_begin
@@ -36,30 +40,30 @@ __global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, i
     }
     seq = lo; seq_start = a.cu_seqlens[seq]; seq_end = a.cu_seqlens[seq + 1];
   }
-  auto load8 = [&](int t, float (&f)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(xg + (int64_t)t * a.x_stride_t);
-    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
-    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
-    f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xffff0000u);
-    f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xffff0000u);
+  auto unpack = [](uint4 raw, float2 (&f)[4]) {
+    f[0] = bf16x2_to_float2(raw.x); f[1] = bf16x2_to_float2(raw.y);
+    f[2] = bf16x2_to_float2(raw.z); f[3] = bf16x2_to_float2(raw.w);
   };
-  float hist[WIDTH][8];  // hist[WIDTH-1] is the current token
+  float2 hist[WIDTH][4];  // hist[WIDTH-1] is the current token
 #pragma unroll
   for (int j = 0; j < WIDTH - 1; ++j) {
     const int t = t_begin - (WIDTH - 1) + j;
     if (t >= seq_start && t >= 0) {
-      load8(t, hist[j]);
+      unpack(*reinterpret_cast<const uint4*>(xg + (int64_t)t * a.x_stride_t), hist[j]);
     } else {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
+      for (int c = 0; c < 4; ++c) hist[j][c] = make_float2(0.f, 0.f);
     }
   }
+  const __nv_bfloat16* xp = xg + (int64_t)t_begin * a.x_stride_t;
+  __nv_bfloat16* yp = yg + (int64_t)t_begin * a.y_stride_t;
   // tokens are fetched eight at a time so that eight 16-byte loads are in flight per thread
   for (int tb = t_begin; tb < t_end; tb += 8) {
     uint4 raw[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      raw[j] = (tb + j < t_end) ? *reinterpret_cast<const uint4*>(xg + (int64_t)(tb + j) * a.x_stride_t) : make_uint4(0u, 0u, 0u, 0u);
+      raw[j] = (tb + j < t_end) ? *reinterpret_cast<const uint4*>(xp + (int64_t)j * a.x_stride_t) : make_uint4(0u, 0u, 0u, 0u);
+    xp += 8 * a.x_stride_t;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int t = tb + j;
@@ -69,29 +73,24 @@ __global__ void __launch_bounds__(256) conv1d_silu_kernel(const AveConvArgs a, i
 #pragma unroll
         for (int jj = 0; jj < WIDTH - 1; ++jj)
 #pragma unroll
-          for (int c = 0; c < 8; ++c) hist[jj][c] = 0.f;
+          for (int c = 0; c < 4; ++c) hist[jj][c] = make_float2(0.f, 0.f);
       }
-      const uint4 rw = raw[j];
-      float* cur = hist[WIDTH - 1];
-      cur[0] = __uint_as_float(rw.x << 16); cur[1] = __uint_as_float(rw.x & 0xffff0000u);
-      cur[2] = __uint_as_float(rw.y << 16); cur[3] = __uint_as_float(rw.y & 0xffff0000u);
-      cur[4] = __uint_as_float(rw.z << 16); cur[5] = __uint_as_float(rw.z & 0xffff0000u);
-      cur[6] = __uint_as_float(rw.w << 16); cur[7] = __uint_as_float(rw.w & 0xffff0000u);
-      float out[8];
+      unpack(raw[j], hist[WIDTH - 1]);
+      uint32_t packed[4];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float acc = bias[c];
+      for (int c = 0; c < 4; ++c) {
+        float2 acc = bias[c];
 #pragma unroll
-        for (int jj = 0; jj < WIDTH; ++jj) acc = fmaf(w[c][jj], hist[jj][c], acc);
-        out[c] = silu(acc);
+        for (int jj = 0; jj < WIDTH; ++jj) acc = __ffma2_rn(w[c][jj], hist[jj][c], acc);
+        const float2 o = silu2(acc);
+        packed[c] = pack_bf16x2(o.x, o.y);
       }
-      const uint4 packed = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]),
-                                      pack_bf16x2(out[4], out[5]), pack_bf16x2(out[6], out[7]));
-      *reinterpret_cast<uint4*>(yg + (int64_t)t * a.y_stride_t) = packed;
+      *reinterpret_cast<uint4*>(yp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      yp += a.y_stride_t;
 #pragma unroll
       for (int jj = 0; jj < WIDTH - 1; ++jj)
 #pragma unroll
-        for (int c = 0; c < 8; ++c) hist[jj][c] = hist[jj + 1][c];
+        for (int c = 0; c < 4; ++c) hist[jj][c] = hist[jj + 1][c];
     }
   }
 }

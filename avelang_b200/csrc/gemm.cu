@@ -27,7 +27,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int mt, int nt) {
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    __nv_bfloat16* __restrict__ C, int64_t M, int64_t N, int64_t K, int64_t ldc, uint32_t* status) {
+                    __nv_bfloat16* __restrict__ C, int64_t M, int64_t N, int64_t K, int64_t ldc, uint32_t* status, int bn) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -39,7 +39,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = (int)((M + BM - 1) / BM), nt = (int)((N + BN - 1) / BN), kb_count = (int)((K + BK - 1) / BK);
+  // bn: width of a column tile, a multiple of 16 up to BN chosen by the launcher so that the column tiles are of
+  // (nearly) equal width; shared memory and tensor memory are laid out for BN
+  const int mt = (int)((M + BM - 1) / BM), nt = (int)((N + bn - 1) / bn), kb_count = (int)((K + BK - 1) / BK);
   const int n_tiles = mt * nt;
 
   if (threadIdx.x == 0) {
@@ -63,9 +65,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const TileCoord tcd = tile_coord(tile, mt, nt);
         for (int kb = 0; kb < kb_count; ++kb) {
           if (!tc::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) goto producer_done;
-          tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+          tc::mbar_expect_tx(&full[s], (uint32_t)(A_BYTES + bn * BK * 2));
           tc::tma_load_2d(smem + s * STAGE_BYTES, &tmA, &full[s], kb * BK, tcd.m * BM);
-          tc::tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &tmB, &full[s], kb * BK, tcd.n * BN);
+          tc::tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &tmB, &full[s], kb * BK, tcd.n * bn);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -75,11 +77,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; int local = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-        // a ragged last column tile issues MMAs only as wide as the columns that exist (N of the instruction in steps of
-        // 16): with N = 1544 the seventh tile is 8 columns wide and costs a sixteenth of a full one on the tensor pipe
-        const int64_t n_left = N - (int64_t)tile_coord(tile, mt, nt).n * BN;
-        const int n_mma = n_left >= BN ? BN : (int)((n_left + 15) / 16) * 16;
-        const uint32_t idesc = tc::idesc_f16(BM, n_mma, 1, 1, false, false);
+        const uint32_t idesc = tc::idesc_f16(BM, bn, 1, 1, false, false);
         const int buf = local & 1;
         const uint32_t acc_ph = (uint32_t)(local >> 1) & 1u;
         if (!tc::mbar_wait(&acc_empty[buf], acc_ph ^ 1u, abort_flag)) break;
@@ -113,9 +111,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!tc::mbar_wait(&acc_full[buf], acc_ph, abort_flag)) break;
       tc::tc_fence_after_sync();
       const int64_t row = (int64_t)tcd.m * BM + quarter * 32 + lane;
-      __nv_bfloat16* crow = C + row * ldc + (int64_t)tcd.n * BN;
-      const int64_t n_left = N - (int64_t)tcd.n * BN;
-      const int col_groups = n_left >= BN ? BN / 32 : (int)((n_left + 31) / 32);  // 32-column groups that hold results
+      __nv_bfloat16* crow = C + row * ldc + (int64_t)tcd.n * bn;
+      const int64_t n_left = min((int64_t)bn, N - (int64_t)tcd.n * bn);
+      const int col_groups = (int)((n_left + 31) / 32);  // 32-column groups that hold results
 #pragma unroll 1
       for (int c = 0; c < col_groups; ++c) {
         uint32_t r[32];
@@ -160,7 +158,12 @@ int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   const uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M}, strA[2] = {2, (uint64_t)a.lda * 2};
   const uint64_t dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N}, strB[2] = {2, (uint64_t)a.ldb * 2};
-  const uint32_t boxA[2] = {BK, BM}, boxB[2] = {BK, BN};
+  // Column tiles of equal width: as few tiles as BN = 256 allows, each as narrow as that count permits (a multiple of
+  // 16, the granularity of the MMA's N).  N = 1544 becomes 7 tiles of 224 columns instead of 6 of 256 and one of 8,
+  // whose MMAs and A-tile loads would be spent on 8 columns of output.
+  const int64_t n_tiles_n = (a.N + BN - 1) / BN;
+  const int bn = (int)(((a.N + n_tiles_n - 1) / n_tiles_n + 15) / 16 * 16);
+  const uint32_t boxA[2] = {BK, BM}, boxB[2] = {BK, (uint32_t)bn};
   int rc = make_tmap(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.a), 2, dimsA, strA, boxA, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != AVE_GDN_OK) return rc;
   rc = make_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.b), 2, dimsB, strB, boxB, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -174,10 +177,10 @@ int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream) {
   }
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  const int64_t tiles = ((a.M + BM - 1) / BM) * ((a.N + bn - 1) / bn);
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
   gemm_bf16_nt_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, reinterpret_cast<__nv_bfloat16*>(a.c), a.M, a.N, a.K,
-                                                               a.ldc, a.status);
+                                                               a.ldc, a.status, bn);
   AVE_CUDA_TRY(cudaGetLastError());
   return AVE_GDN_OK;
 }

@@ -589,6 +589,11 @@ def profile_case(name: str):
         w = (torch.randn(8192, 4, device="cuda") / 2).bfloat16()
         for _ in range(3):
             gdn.causal_conv1d_silu(x, w)
+    elif name == "norm":
+        x = torch.randn(32768, 32, 128, device="cuda").bfloat16()  # 256 MiB per tensor
+        z = torch.randn(32768, 32, 128, device="cuda").bfloat16()
+        for _ in range(3):
+            gdn.gated_rmsnorm(x, z)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     torch.cuda.synchronize()
@@ -607,7 +612,7 @@ def main():
     ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block", "helpers"],
                     help="prefill (default, the headline line), varlen (head-sharded packed prefill), block, or helpers "
                          "(GEMM, conv1d, norm and gate kernels timed alone on one GPU)")
-    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k", "gemm1544", "conv"],
+    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k", "gemm1544", "conv", "norm"],
                     help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
     if args.profile_case:
