@@ -61,6 +61,16 @@ class DecodeLayerArgs(ctypes.Structure):
                 + [("proj_stride", I64), ("o_stride", I64), ("scale", F32), ("norm_eps", F32)])
 
 
+class BwdArgs(ctypes.Structure):
+    _fields_ = ([("struct_size", U32), ("flags", U32)]
+                + [(n, P) for n in ("q", "k", "v", "g", "beta", "d_o", "initial_state", "d_final_state", "cu_seqlens", "d_q", "d_k",
+                                    "d_v", "d_g", "d_beta", "d_initial_state", "status", "workspace")]
+                + [("workspace_bytes", U64)]
+                + [(n, I32) for n in ("B", "T", "Hk", "Hv", "dk", "dv", "n_seqs", "reserved0")]
+                + [(f"{t}_stride_{d}", I64) for t in ("q", "k", "v", "do") for d in ("b", "t", "h")]
+                + [("g_stride_b", I64), ("g_stride_t", I64), ("scale", F32), ("reserved1", F32)])
+
+
 class GateArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("A_log", P), ("dt_bias", P),
                 ("g", P), ("beta", P), ("rows", I64), ("Hv", I32), ("reserved0", I32),
@@ -80,6 +90,8 @@ SYMBOLS = {
     "ave_gdn_conv1d_update": (ctypes.c_int, [ctypes.POINTER(ConvUpdateArgs), P]),
     "ave_gdn_gate_beta": (ctypes.c_int, [ctypes.POINTER(GateArgs), P]),
     "ave_gdn_decode_layer_step": (ctypes.c_int, [ctypes.POINTER(DecodeLayerArgs), P]),
+    "ave_gdn_recurrent_backward": (ctypes.c_int, [ctypes.POINTER(BwdArgs), P]),
+    "ave_gdn_backward_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(BwdArgs)]),
     "ave_gdn_abi_version": (ctypes.c_int, []),
     "ave_gdn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ave_gdn_last_cuda_error": (ctypes.c_int, []),

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libave_gdn_b200.so")
-SOURCES = ["api.cu", "decode.cu", "decode_layer.cu", "rmsnorm.cu", "prefill_simt.cu", "elementwise.cu", "gemm.cu", "tmap.cu", "prefill_tc.cu"]
+SOURCES = ["api.cu", "decode.cu", "decode_layer.cu", "backward.cu", "rmsnorm.cu", "prefill_simt.cu", "elementwise.cu", "gemm.cu", "tmap.cu", "prefill_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE,
               "-I" + CSRC]

@@ -17,6 +17,8 @@ int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
 int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
 int launch_decode_layer(const AveGdnDecodeLayerArgs& a, cudaStream_t stream);
+int launch_backward(const AveGdnBwdArgs& a, cudaStream_t stream);
+size_t backward_workspace_bytes(const AveGdnBwdArgs& a);
 
 static size_t prefill_ws_bytes(const AveGdnArgs& a) {
   return a.dk == 128 ? prefill_tc_workspace_bytes(a, false) : prefill_simt_workspace_bytes(a);
@@ -139,6 +141,40 @@ int ave_gdn_conv1d_update(const AveConvUpdateArgs* a, void* stream) {
   if (a->state_indices == nullptr && a->num_slots < a->n_seqs) return AVE_GDN_INVALID_ARGUMENT;
   if (!aligned16(a->x) || !aligned16(a->y) || !aligned16(a->conv_state) || (a->x_stride % 8) || (a->y_stride % 8)) return AVE_GDN_MISALIGNED;
   return launch_conv1d_update(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int validate_bwd(const AveGdnBwdArgs* a) {
+  if (a == nullptr || a->struct_size != sizeof(AveGdnBwdArgs)) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->B < 0 || a->T < 0 || a->n_seqs < 0 || a->Hk <= 0 || a->Hv <= 0 || a->Hv % a->Hk != 0) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->dk != 128 || a->dv != 128) return AVE_GDN_UNSUPPORTED;
+  if (a->cu_seqlens != nullptr && a->B != 1) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->cu_seqlens == nullptr && a->n_seqs != a->B) return AVE_GDN_INVALID_ARGUMENT;
+  if ((int64_t)a->B * a->T == 0 || a->n_seqs == 0) return AVE_GDN_OK;
+  if (!a->q || !a->k || !a->v || !a->g || !a->beta || !a->d_o || !a->d_q || !a->d_k || !a->d_v || !a->d_g || !a->d_beta) return AVE_GDN_INVALID_ARGUMENT;
+  int rc;
+  if ((rc = check_rows(a->q, a->q_stride_t, a->q_stride_h, a->q_stride_b, 2))) return rc;
+  if ((rc = check_rows(a->k, a->k_stride_t, a->k_stride_h, a->k_stride_b, 2))) return rc;
+  if ((rc = check_rows(a->v, a->v_stride_t, a->v_stride_h, a->v_stride_b, 2))) return rc;
+  if ((rc = check_rows(a->d_o, a->do_stride_t, a->do_stride_h, a->do_stride_b, 2))) return rc;
+  if (!aligned16(a->d_q) || !aligned16(a->d_k) || !aligned16(a->d_v)) return AVE_GDN_MISALIGNED;
+  if ((a->initial_state && !aligned16(a->initial_state)) || (a->d_final_state && !aligned16(a->d_final_state)) ||
+      (a->d_initial_state && !aligned16(a->d_initial_state)))
+    return AVE_GDN_MISALIGNED;
+  return AVE_GDN_OK;
+}
+
+size_t ave_gdn_backward_workspace_bytes(const AveGdnBwdArgs* a) {
+  if (validate_bwd(a) != AVE_GDN_OK) return 0;
+  return backward_workspace_bytes(*a);
+}
+
+int ave_gdn_recurrent_backward(const AveGdnBwdArgs* a, void* stream) {
+  const int rc = validate_bwd(a);
+  if (rc != AVE_GDN_OK) return rc;
+  if ((int64_t)a->B * a->T == 0 || a->n_seqs == 0) return AVE_GDN_OK;
+  if (a->workspace == nullptr || !aligned16(a->workspace)) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->workspace_bytes < backward_workspace_bytes(*a)) return AVE_GDN_WORKSPACE_TOO_SMALL;
+  return launch_backward(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ave_gdn_decode_layer_step(const AveGdnDecodeLayerArgs* a, void* stream) {

@@ -24,7 +24,7 @@ import torch
 from . import _lib, torch_ops
 
 __all__ = ["chunk_gated_delta_rule", "fused_recurrent_gated_delta_rule", "mixed_prefill_decode_step", "gated_rmsnorm",
-           "causal_conv1d_silu", "causal_conv1d_update", "gate_beta", "decode_layer_step", "prefill_launch_count", "read_status"]
+           "causal_conv1d_silu", "causal_conv1d_update", "gate_beta", "decode_layer_step", "gated_delta_rule_backward", "GatedDeltaRuleFunction", "prefill_launch_count", "read_status"]
 
 _status_words: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -309,6 +309,78 @@ def mixed_prefill_decode_step(q, k, v, g, beta, cu_seqlens, n_decode, state_pool
                                norm_weight=norm_weight, norm_eps=norm_eps, state_indices=state_indices[nd:].contiguous(),
                                out=rest(o))
     return o
+
+
+def gated_delta_rule_backward(q, k, v, g, beta, d_o, scale=None, initial_state=None, d_final_state=None, cu_seqlens=None):
+    """Gradients of ``chunk_gated_delta_rule`` / ``fused_recurrent_gated_delta_rule`` (without the in-kernel L2 norm and
+    without the fused gated norm) for d = 128.  ``d_o``: bf16, shaped like ``v``; ``d_final_state``: optional fp32 gradient
+    of the final states.  Returns ``(dq, dk, dv, dg, dbeta, d_initial_state)``: dq, dk in the dtype and shape of q, k (the
+    value heads sharing a key head are summed), dv in the dtype of v, dg, dbeta fp32, ``d_initial_state`` fp32 or None
+    when no initial state was given.  A token-by-token reverse sweep in fp32 (recomputing the states from 64-token
+    checkpoints): exact to fp32 rounding, and far slower than the chunked forward pass."""
+    B, T, Hk, Hv, dk, dv, n_seqs = _check_common(q, k, v, g, beta, None, cu_seqlens)
+    _req((dk, dv) == (128, 128), f"the backward pass is built for head dims (128, 128), got {(dk, dv)}.")
+    _req(d_o.dtype == torch.bfloat16 and d_o.shape == v.shape and d_o.device == q.device and d_o.stride(-1) == 1,
+         f"d_o must be a bf16 tensor of shape {tuple(v.shape)} on {q.device}")
+    for name, t in (("initial_state", initial_state), ("d_final_state", d_final_state)):
+        if t is not None:
+            _req(t.dtype == torch.float32 and tuple(t.shape) == (n_seqs, Hv, dk, dv) and t.is_contiguous() and t.device == q.device,
+                 f"{name} must be a contiguous fp32 tensor ({n_seqs}, {Hv}, {dk}, {dv}) on {q.device}")
+    f32 = dict(dtype=torch.float32, device=q.device)
+    dq_v, dk_v = torch.empty(B, T, Hv, dk, **f32), torch.empty(B, T, Hv, dk, **f32)
+    dv_f, dg, dbeta = torch.empty(B, T, Hv, dv, **f32), torch.empty(B, T, Hv, **f32), torch.empty(B, T, Hv, **f32)
+    ds0 = torch.empty(n_seqs, Hv, dk, dv, **f32) if initial_state is not None else None
+    torch_ops.op("recurrent_backward")(q, k, v, g, beta, d_o, float(dk ** -0.5 if scale is None else scale), initial_state,
+                                       d_final_state, cu_seqlens, dq_v, dk_v, dv_f, dg, dbeta, ds0)
+    r = Hv // Hk
+    dq = dq_v.view(B, T, Hk, r, dk).sum(3).to(q.dtype)
+    dk_ = dk_v.view(B, T, Hk, r, dk).sum(3).to(k.dtype)
+    return dq, dk_, dv_f.to(v.dtype), dg, dbeta, ds0
+
+
+@torch_ops.implement("recurrent_backward")
+def _recurrent_backward(q, k, v, g, beta, d_o, scale, initial_state, d_final_state, cu_seqlens, dq, dk, dv, dg, dbeta, d_initial_state):
+    """torch.ops.avelang_gdn.recurrent_backward -> ave_gdn_recurrent_backward on the current stream."""
+    B, T, Hk, dkk = q.shape
+    Hv, dvv = v.shape[2], v.shape[3]
+    a = _lib.BwdArgs()
+    a.struct_size = ctypes.sizeof(_lib.BwdArgs)
+    ptr = lambda t: t.data_ptr() if t is not None and t.numel() > 0 else None
+    a.q, a.k, a.v, a.g, a.beta, a.d_o = ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(d_o)
+    a.initial_state, a.d_final_state, a.cu_seqlens = ptr(initial_state), ptr(d_final_state), ptr(cu_seqlens)
+    a.d_q, a.d_k, a.d_v, a.d_g, a.d_beta, a.d_initial_state = ptr(dq), ptr(dk), ptr(dv), ptr(dg), ptr(dbeta), ptr(d_initial_state)
+    a.status = _status_word(q.device).data_ptr()
+    a.B, a.T, a.Hk, a.Hv, a.dk, a.dv = B, T, Hk, Hv, dkk, dvv
+    a.n_seqs = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    for name, t in (("q", q), ("k", k), ("v", v), ("do", d_o)):
+        setattr(a, f"{name}_stride_b", t.stride(0)); setattr(a, f"{name}_stride_t", t.stride(1)); setattr(a, f"{name}_stride_h", t.stride(2))
+    a.g_stride_b, a.g_stride_t, a.scale = g.stride(0), g.stride(1), float(scale)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, lib.ave_gdn_backward_workspace_bytes(ctypes.byref(a)))
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        rc = lib.ave_gdn_recurrent_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "gated_delta_rule_backward")
+
+
+class GatedDeltaRuleFunction(torch.autograd.Function):
+    """``o, final_state = GatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state)``: the chunked forward pass
+    with the reverse-sweep backward pass attached (d = 128, dense batches, no in-kernel L2 norm, no fused gated norm)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state):
+        o, final = chunk_gated_delta_rule(q, k, v, g, beta, scale, initial_state, output_final_state=True)
+        ctx.save_for_backward(q, k, v, g, beta, initial_state if initial_state is not None else torch.empty(0, device=q.device))
+        ctx.scale, ctx.has_state = scale, initial_state is not None
+        return o, final
+
+    @staticmethod
+    def backward(ctx, d_o, d_final):
+        q, k, v, g, beta, s0 = ctx.saved_tensors
+        d_o = torch.zeros_like(v) if d_o is None else d_o.to(torch.bfloat16).contiguous()
+        d_final = None if d_final is None else d_final.float().contiguous()
+        dq, dk, dv, dg, dbeta, ds0 = gated_delta_rule_backward(q, k, v, g, beta, d_o, ctx.scale, s0 if ctx.has_state else None, d_final)
+        return dq, dk, dv, dg, dbeta, None, ds0
 
 
 def decode_layer_step(proj, conv_weight, conv_state, A_log, dt_bias, state_pool, state_indices=None, *, Hk, Hv, conv_bias=None,

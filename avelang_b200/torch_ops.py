@@ -24,6 +24,9 @@ SCHEMAS = {
     "conv1d_update": "(Tensor x, Tensor(a!) conv_state, Tensor weight, Tensor? bias, Tensor? state_indices, Tensor(b!) out) -> ()",
     "gate_beta": "(Tensor a, Tensor b, Tensor A_log, Tensor dt_bias, Tensor(a!) g, Tensor(b!) beta) -> ()",
     "gemm_bf16_nt": "(Tensor A, Tensor B, Tensor(a!) out) -> ()",
+    "recurrent_backward": "(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor d_o, float scale, Tensor? initial_state, "
+                          "Tensor? d_final_state, Tensor? cu_seqlens, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) dg, "
+                          "Tensor(e!) dbeta, Tensor(f!)? d_initial_state) -> ()",
     "decode_layer_step": "(Tensor proj, Tensor conv_w, Tensor? conv_bias, Tensor(a!) conv_state, Tensor A_log, Tensor dt_bias, "
                          "Tensor? norm_weight, Tensor(b!) state_pool, Tensor? state_indices, Tensor(c!) out, int Hk, int Hv, "
                          "float scale, float norm_eps, bool gate_first) -> ()",

@@ -266,7 +266,9 @@ def bench_prefill(args, rank, world):
 
 def bench_decode(steps=1000, warmup=20):
     """256 sequences x 32 heads, one token each, state pool of 512 fp32 slots updated in place; a ring of 8
-    pre-generated q/k/v/g/beta sets so the small inputs are not replayed from cache."""
+    pre-generated q/k/v/g/beta sets so the small inputs are not replayed from cache.  Also the same step with the
+    layer's front end fused in (conv update, L2 norms, gate/beta, gated norm from the projection row: one kernel) next
+    to the separate kernels it replaces."""
     from avelang_b200 import gdn, synth
     base = synth.config2().to("cuda")
     ring = [synth.config2(seed=100 + i).to("cuda") for i in range(8)]
@@ -277,19 +279,46 @@ def bench_decode(steps=1000, warmup=20):
         r = ring[i % 8]
         gdn.fused_recurrent_gated_delta_rule(r.q, r.k, r.v, r.g, r.beta, initial_state=pool, state_indices=idx, out=out)
 
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(steps):
-        step(i)
-    b.record()
-    torch.cuda.synchronize()
-    us = a.elapsed_time(b) * 1e3 / steps
+    def timed(fn, n):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / n
+
+    us = timed(step, steps)
     state_bytes = 256 * HV * D * D * 4 * 2
     other = 256 * (HK * D * 2 * 2 + HV * D * 2 * 2 + HV * 4 * 2 + 4)
-    return us, state_bytes, state_bytes + other
+    # the whole layer step from the in-projection row: fused kernel vs conv update + gate/beta + decode step
+    Cn, cols, N = 2 * HK * D + HV * D, 2 * HK * D + 2 * HV * D + 2 * HV, 256
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    projs = [torch.randn(N, cols, device="cuda", generator=gen).bfloat16() for _ in range(8)]
+    conv_w = (torch.randn(Cn, 4, device="cuda", generator=gen) / 2).bfloat16()
+    conv_state = torch.randn(512, 3, Cn, device="cuda", generator=gen).bfloat16()
+    A_log, dt_bias = torch.rand(HV, device="cuda") * 2.77, torch.randn(HV, device="cuda") * 0.1
+    o2 = torch.empty(N, HV, D, dtype=torch.bfloat16, device="cuda")
+
+    def fused(i):
+        gdn.decode_layer_step(projs[i % 8], conv_w, conv_state, A_log, dt_bias, pool, idx, Hk=HK, Hv=HV, out=o2)
+
+    def separate(i):
+        p = projs[i % 8]
+        qkv = gdn.causal_conv1d_update(p[:, :Cn], conv_state, conv_w, state_indices=idx)
+        g, beta = gdn.gate_beta(p[:, cols - HV:], p[:, cols - 2 * HV:cols - HV], A_log, dt_bias)
+        gdn.fused_recurrent_gated_delta_rule(qkv[:, :HK * D].reshape(N, 1, HK, D), qkv[:, HK * D:2 * HK * D].reshape(N, 1, HK, D),
+                                             qkv[:, 2 * HK * D:].reshape(N, 1, HV, D), g.reshape(N, 1, HV), beta.reshape(N, 1, HV),
+                                             initial_state=pool, state_indices=idx, use_qk_l2norm_in_kernel=True,
+                                             z=p[:, Cn:Cn + HV * D].reshape(N, 1, HV, D), out=o2.reshape(N, 1, HV, D))
+
+    layer = {"fused_us_per_step": timed(fused, 200), "separate_kernels_us_per_step": timed(separate, 200),
+             "what": "decode step of the whole layer behind its in-projection (conv update + SiLU, q/k L2 norm, gate/beta, "
+                     "delta-rule update, gated norm): one kernel vs the three separate entry points"}
+    return us, state_bytes, state_bytes + other, layer
 
 
 def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0, n_seqs=1):
@@ -661,10 +690,11 @@ def main():
                         "hbm_view": {"achieved_gbs": algo_bytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                                      "algorithmic_bytes": algo_bytes}}
     if rank == 0 and not args.no_decode:
-        us, state_bytes, all_bytes = bench_decode()
+        us, state_bytes, all_bytes, layer_step = bench_decode()
         line["decode"] = {"metric": "gdn_decode_state_GBps", "value": state_bytes / (us * 1e-6) / 1e9, "unit": "GB/s",
                           "us_per_step": us, "steps": 1000,
                           "config": {"workload": "256 seqs x 32 value heads, T=1, 512-slot fp32 pool [128x128], in place"},
+                          "layer_step": layer_step,
                           "roofline": {"bound": "hbm", "achieved": all_bytes / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": all_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
                                        "frac_of_nominal_8TBps": all_bytes / (us * 1e-6) / 8e12,

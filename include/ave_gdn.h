@@ -216,6 +216,45 @@ typedef struct AveGdnDecodeLayerArgs {
 } AveGdnDecodeLayerArgs;
 int ave_gdn_decode_layer_step(const AveGdnDecodeLayerArgs* args, void* stream);
 
+/* Backward pass of the recurrence (dk = dv = 128; q and k as given, i.e. without the in-kernel L2 norm, and without the
+ * fused gated norm: those two are differentiated by the caller's framework around this call).  Inputs as for the
+ * forward pass plus d_o (bf16, laid out like v) and the optional gradient of the final states; outputs in fp32:
+ * dq, dk [B,T,Hv,dk] PER VALUE HEAD (the caller sums the value heads that share a key head), dv [B,T,Hv,dv],
+ * dg, dbeta [B,T,Hv], and optionally d_initial_state [n_seqs,Hv,dk,dv]; all contiguous.  Token-by-token reverse sweep
+ * in fp32 with the state recomputed from 64-token checkpoints held in `workspace`. */
+typedef struct AveGdnBwdArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* q;  /* bf16 */
+  const void* k;  /* bf16 */
+  const void* v;  /* bf16 */
+  const float* g;
+  const float* beta;
+  const void* d_o;                /* bf16 [B,T,Hv,dv] */
+  const float* initial_state;     /* optional fp32 [n_seqs,Hv,dk,dv] */
+  const float* d_final_state;     /* optional fp32 [n_seqs,Hv,dk,dv] */
+  const int32_t* cu_seqlens;      /* optional int32 [n_seqs+1]; requires B == 1 */
+  float* d_q;                     /* fp32 [B,T,Hv,dk], per value head */
+  float* d_k;                     /* fp32 [B,T,Hv,dk], per value head */
+  float* d_v;                     /* fp32 [B,T,Hv,dv] */
+  float* d_g;                     /* fp32 [B,T,Hv] */
+  float* d_beta;                  /* fp32 [B,T,Hv] */
+  float* d_initial_state;         /* optional */
+  uint32_t* status;
+  void* workspace;                /* >= ave_gdn_backward_workspace_bytes() */
+  uint64_t workspace_bytes;
+  int32_t B, T, Hk, Hv, dk, dv, n_seqs, reserved0;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  int64_t do_stride_b, do_stride_t, do_stride_h;
+  int64_t g_stride_b, g_stride_t;
+  float scale;
+  float reserved1;
+} AveGdnBwdArgs;
+int ave_gdn_recurrent_backward(const AveGdnBwdArgs* args, void* stream);
+size_t ave_gdn_backward_workspace_bytes(const AveGdnBwdArgs* args);
+
 /* g = -exp(A_log[h]) * softplus(a + dt_bias[h]),  beta = sigmoid(b);  a,b bf16 [rows,Hv] (strided),
  * A_log,dt_bias fp32 [Hv];  g,beta fp32 [rows,Hv] contiguous. */
 typedef struct AveGateArgs {

@@ -227,3 +227,16 @@ def rel_l2(x: torch.Tensor, ref: torch.Tensor) -> float:
     x, ref = x.double(), ref.double()
     den = ref.norm().item()
     return (x - ref).norm().item() / (den if den > 0 else 1.0)
+
+
+def recurrent_grads(q, k, v, g, beta, d_o, scale=None, initial_state=None, d_final_state=None, cu_seqlens=None):
+    """Gradients of the token recurrence by automatic differentiation of ``naive_recurrent_gated_delta_rule`` in fp64:
+    returns (dq, dk, dv, dg, dbeta, d_initial_state or None) for the cotangents ``d_o`` (of o) and ``d_final_state``."""
+    leaves = [t.detach().double().requires_grad_(True) for t in (q, k, v, g, beta)]
+    s0 = initial_state.detach().double().requires_grad_(True) if initial_state is not None else None
+    o, final = naive_recurrent_gated_delta_rule(*leaves, scale, s0, cu_seqlens)
+    loss = (o * d_o.double()).sum()
+    if d_final_state is not None:
+        loss = loss + (final * d_final_state.double()).sum()
+    grads = torch.autograd.grad(loss, leaves + ([s0] if s0 is not None else []))
+    return (*grads[:5], grads[5] if s0 is not None else None)
