@@ -21,23 +21,6 @@ namespace {
 
 constexpr int BD = 128, BW = 8, BROWS = BD / BW, BCH = 64;  // head dim, warps, rows per warp, tokens per checkpoint
 
-// Butterfly reduction of 32 per-lane values over the 32 lanes: on return lane l holds the sum over all lanes of v[l].
-__device__ __forceinline__ float reduce32(float (&v)[32], int lane) {
-#pragma unroll
-  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
-    const bool upper = (lane & s) != 0;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      if (i < n / 2) {
-        const float send = upper ? v[i] : v[i + n / 2];
-        const float keep = upper ? v[i + n / 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
-      }
-    }
-  }
-  return v[0];
-}
-
 struct Tok {
   float alpha, beta;
   float v4[4], do4[4];

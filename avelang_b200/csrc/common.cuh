@@ -44,6 +44,23 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
+// Butterfly reduction of 32 per-lane values over the 32 lanes: on return lane l holds the sum over all lanes of v[l].
+__device__ __forceinline__ float reduce32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i < n / 2) {
+        const float send = upper ? v[i] : v[i + n / 2];
+        const float keep = upper ? v[i + n / 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+      }
+    }
+  }
+  return v[0];
+}
+
 __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // silu of two values with the multiplies and the add as packed fp32 pairs (one instruction per pair); the exponential

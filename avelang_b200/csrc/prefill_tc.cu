@@ -1130,15 +1130,19 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 // Once every chain of a multi-part sequence has run, the carry buffer holds, per (sequence, value head): chain 0 = the
 // true state after part 0, chain 2p-1 = the end state Psi_p of part p's local chain, chain 2p = part p's transition
 // matrix F_p (row-major [k][d]: M_end = F_p M0 + Psi_p).
-// Serial combine over the parts of one (sequence, value head, 16-column slice of d_v): M0(1) = state after part 0,
-// M0(p+1) = F_p M0(p) + Psi_p in fp32 on the CUDA cores (a few 128x128x16 products); the last one is the sequence's
-// final state.  M0(p) for p >= 2 also leaves as the bf16 hi/lo operand image the fix-up kernel's MMAs read (B[d_v][k]);
-// the image of M0(1) was written by the scan itself.
-constexpr int COMBINE_COLS = 16;
+// Serial combine over the parts of one (sequence, value head, 8-column slice of d_v): M0(1) = state after part 0,
+// M0(p+1) = F_p M0(p) + Psi_p in fp32 on the CUDA cores; the last one is the sequence's final state.  M0(p) for p >= 2
+// also leaves as the bf16 hi/lo operand image the fix-up kernel's MMAs read (B[d_v][k]); the image of M0(1) was written
+// by the scan itself.  The steps are serial, so each is kept short: F_p is staged in shared memory with coalesced loads
+// (row pitch 129: a thread walks its own row without bank conflicts) and the tile of the next step is already in
+// registers while the current one is multiplied.
+constexpr int COMBINE_COLS = 8, COMBINE_PITCH = 129;
+constexpr size_t COMBINE_SMEM = (size_t)D * COMBINE_PITCH * 4;
 __global__ void __launch_bounds__(256)
 part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ carry,
                     uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
-  __shared__ float cur[2][D][COMBINE_COLS];
+  extern __shared__ float Fs[];  // [D][COMBINE_PITCH]
+  __shared__ __align__(16) float cur[2][D][COMBINE_COLS];
   const int cb = blockIdx.x, h = blockIdx.y, n = blockIdx.z, tid = threadIdx.x;
   if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;
   const SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, nullptr);
@@ -1156,39 +1160,42 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
     const float* src = tile_of(0);
     for (int e = tid; e < D * COMBINE_COLS; e += 256) cur[0][e / COMBINE_COLS][e % COMBINE_COLS] = src[(e / COMBINE_COLS) * D + cb * COMBINE_COLS + e % COMBINE_COLS];
   }
+  // a thread fetches 16 float4 of the 128x128 tile: element 4 * (tid + 256 i), i.e. row (tid + 256 i) / 32
+  float4 pre[16];
+  auto fetch = [&](int p) {
+    const float4* F4 = reinterpret_cast<const float4*>(tile_of(2 * p));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pre[i] = F4[tid + 256 * i];
+  };
+  fetch(1);
   int b = 0;
   for (int p = 1; p < active; ++p) {
+    __syncthreads();  // the previous step's readers of Fs are done
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = 4 * (tid + 256 * i), row = e >> 7, c0 = e & 127;
+      float* dst = Fs + row * COMBINE_PITCH + c0;
+      dst[0] = pre[i].x; dst[1] = pre[i].y; dst[2] = pre[i].z; dst[3] = pre[i].w;
+    }
+    if (p + 1 < active) fetch(p + 1);
     __syncthreads();
-    {  // next = F_p cur + Psi_p: a thread owns one row k and eight columns
-      const int k = tid >> 1, j0 = (tid & 1) * 8;
-      const float* F = tile_of(2 * p) + (int64_t)k * D;
-      const float* Psi = tile_of(2 * p - 1) + (int64_t)k * D + cb * COMBINE_COLS + j0;
-      float acc[8];
-      {
-        const float4 p0 = *reinterpret_cast<const float4*>(Psi), p1 = *reinterpret_cast<const float4*>(Psi + 4);
-        acc[0] = p0.x; acc[1] = p0.y; acc[2] = p0.z; acc[3] = p0.w; acc[4] = p1.x; acc[5] = p1.y; acc[6] = p1.z; acc[7] = p1.w;
+    {  // next = F_p cur + Psi_p: a thread owns one row k and four columns
+      const int k = tid >> 1, j0 = (tid & 1) * 4;
+      const float* Frow = Fs + k * COMBINE_PITCH;
+      const float4 psi = *reinterpret_cast<const float4*>(tile_of(2 * p - 1) + (int64_t)k * D + cb * COMBINE_COLS + j0);
+      float acc0 = psi.x, acc1 = psi.y, acc2 = psi.z, acc3 = psi.w;
+#pragma unroll 16
+      for (int d = 0; d < D; ++d) {
+        const float f = Frow[d];
+        const float4 c4 = *reinterpret_cast<const float4*>(&cur[b][d][j0]);
+        acc0 = fmaf(f, c4.x, acc0); acc1 = fmaf(f, c4.y, acc1); acc2 = fmaf(f, c4.z, acc2); acc3 = fmaf(f, c4.w, acc3);
       }
-#pragma unroll 8
-      for (int d4 = 0; d4 < D / 4; ++d4) {
-        const float4 f = *reinterpret_cast<const float4*>(F + 4 * d4);
-        const float fv[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 c0 = *reinterpret_cast<const float4*>(&cur[b][4 * d4 + i][j0]);
-          const float4 c1 = *reinterpret_cast<const float4*>(&cur[b][4 * d4 + i][j0 + 4]);
-          acc[0] = fmaf(fv[i], c0.x, acc[0]); acc[1] = fmaf(fv[i], c0.y, acc[1]);
-          acc[2] = fmaf(fv[i], c0.z, acc[2]); acc[3] = fmaf(fv[i], c0.w, acc[3]);
-          acc[4] = fmaf(fv[i], c1.x, acc[4]); acc[5] = fmaf(fv[i], c1.y, acc[5]);
-          acc[6] = fmaf(fv[i], c1.z, acc[6]); acc[7] = fmaf(fv[i], c1.w, acc[7]);
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) cur[b ^ 1][k][j0 + e] = acc[e];
+      *reinterpret_cast<float4*>(&cur[b ^ 1][k][j0]) = make_float4(acc0, acc1, acc2, acc3);
     }
     b ^= 1;
     __syncthreads();
-    if (p + 1 < active) {  // operand image of M0(p+1): B[row = d_v][k] = M0[k][d_v]; one 16-byte piece of hi and lo per thread
-      const int k8 = tid >> 4, v = tid & 15;
+    if (p + 1 < active && tid < 128) {  // operand image of M0(p+1): B[row = d_v][k] = M0[k][d_v]; a 16-byte piece of hi and of lo
+      const int k8 = tid >> 3, v = tid & 7;
       uint32_t hi[4], lo[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) split_pair(make_float2(cur[b][8 * k8 + 2 * w][v], cur[b][8 * k8 + 2 * w + 1][v]), hi[w], lo[w]);
@@ -1208,24 +1215,28 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
 // Fix-up of the parts after the first.  For 128 tokens (two chunks of one part) of one value head,
 //   o = o_local + qt M0(part)        (qt = the transition chain's rows, [128 tokens][128 d_k])
 // is one 128x128x128 product on tcgen05 with both operands as bf16 hi+lo pairs (hi hi + hi lo + lo hi): A = the qt^T
-// images the scan wrote (MN-major, brought in by bulk copies), B = the image of M0(part).  Then the gated RMSNorm when a
-// gate tensor is given, and the bf16 store.  A CTA serves one (sequence, part, head) and walks every `gridDim.x`-th
-// pair of chunks with B resident: while the threads finish pair i (a thread owns one token row and a quarter of its
-// columns), the product of pair i+1 already runs into the second accumulator and the images of pair i+2 are in flight.
+// images the scan wrote (MN-major, brought in by bulk copies), B = the image of M0(part).  The accumulator (a thread
+// per token row) is staged through shared memory so that everything that touches global memory runs in the layout of
+// the streaming norm kernel: a half-warp per token row, 8 adjacent features per lane, 16- and 32-byte accesses, the
+// RMS over d_v as four shuffles.  (Reading o_local and z straight from the accumulator's layout, a row or a column per
+// thread, measured three to four times slower: 2- or 4-byte accesses and tens of instructions per element.)
+// A CTA serves one (sequence, part, head) and walks every `gridDim.x`-th pair of chunks with the M0 image resident; the
+// images of the next pair are in flight while the current pair's rows are streamed.
 constexpr int FIN_THREADS = 512;
-constexpr int FIN_A = 0, FIN_A_STAGE = 65536, FIN_B = 2 * FIN_A_STAGE, FIN_RED = FIN_B + PACK_BYTES, FIN_BARS = FIN_RED + 2048;
+constexpr int FIN_PITCH = 132;  // floats per staged row: 16-byte aligned rows that spread over the banks
+constexpr int FIN_A = 0, FIN_B = 65536, FIN_STAGE = FIN_B + PACK_BYTES, FIN_BARS = FIN_STAGE + 128 * FIN_PITCH * 4;
 constexpr size_t FIN_SMEM = FIN_BARS + 64 + 1024;
 __global__ void __launch_bounds__(FIN_THREADS, 1)
 part_finish_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, const float* __restrict__ o_f32,
                    const uint8_t* __restrict__ qt_img, const uint8_t* __restrict__ m0_pack, const __grid_constant__ ScanPlan plan) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(smem + FIN_RED);  // [128 rows][4 column quarters]
+  float* stage = reinterpret_cast<float*>(smem + FIN_STAGE);  // [128 tokens][FIN_PITCH] product rows
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FIN_BARS);
   uint64_t* b_bar = bars;
-  uint64_t* a_full = bars + 1;   // [2]
-  uint64_t* mma_bar = bars + 3;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* a_full = bars + 1;
+  uint64_t* mma_bar = bars + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.z / (plan.parts - 1), part = 1 + blockIdx.z % (plan.parts - 1);
@@ -1241,153 +1252,148 @@ part_finish_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start, 
   const int64_t rec0 = a.cu_seqlens ? chunk_start[n] : (int64_t)n * ((a.T + C - 1) / C);  // record of the sequence's chunk 0
   const int stride = gridDim.x;
 
-  auto load_a = [&](int pair, int stage) {  // called by one thread
+  auto load_qt = [&](int pair) {  // called by one thread
     const int c0 = c_begin + 2 * pair, cnt = min(2, c_end - c0);
-    uint8_t* dst = smem + FIN_A + stage * FIN_A_STAGE;
-    tc::mbar_expect_tx(&a_full[stage], (uint32_t)(cnt * QT_BYTES));
+    tc::mbar_expect_tx(a_full, (uint32_t)(cnt * QT_BYTES));
     for (int i = 0; i < cnt; ++i) {
       const uint8_t* img = qt_img + ((rec0 + c0 + i) * a.Hv + h) * (int64_t)QT_BYTES;
-      tc::bulk_load(dst + i * 16384, img, 16384, &a_full[stage]);                   // hi: [chunk 0 | chunk 1]
-      tc::bulk_load(dst + 32768 + i * 16384, img + 16384, 16384, &a_full[stage]);   // lo: [chunk 0 | chunk 1]
+      tc::bulk_load(smem + FIN_A + i * 16384, img, 16384, a_full);                   // hi: [chunk 0 | chunk 1]
+      tc::bulk_load(smem + FIN_A + 32768 + i * 16384, img + 16384, 16384, a_full);   // lo: [chunk 0 | chunk 1]
     }
-  };
-  // warp 0: waits for pair number `it` of this CTA to land and issues its product into accumulator it & 1
-  auto issue_pair = [&](int it, uint32_t tm) -> bool {
-    const int stage = it & 1;
-    bool landed = it > 0 || tc::mbar_wait_warp(b_bar, 0, abort_flag);
-    landed = landed && tc::mbar_wait_warp(&a_full[stage], (uint32_t)(it >> 1) & 1u, abort_flag);
-    tc::tc_fence_after_sync();
-    if (landed && tc::elect_one()) {
-      constexpr uint32_t idesc = tc::idesc_f16(128, 128, 1, 1, true, false);  // A MN-major (token rows), B K-major
-      const uint32_t sa = tc::smem_u32(smem + FIN_A + stage * FIN_A_STAGE), sb = tc::smem_u32(smem + FIN_B);
-#pragma unroll
-      for (int t = 0; t < 3; ++t) {  // hi hi, hi lo, lo hi
-        const uint32_t ab = sa + (t == 2 ? 32768u : 0u), bb = sb + (t == 1 ? 32768u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)  // 16 d_k rows of qt^T per step: 2048 bytes; the two chunks' images lie 16384 bytes apart
-          tc::mma_ss(tm + 128u * (uint32_t)stage, tc::smem_desc_sw128(ab + k * 2048, 16384, 1024),
-                     tc::smem_desc_sw128(bb + (uint32_t)((k >> 2) * 16384 + (k & 3) * 32), 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
-      }
-      tc::mma_commit(&mma_bar[stage]);
-    }
-    __syncwarp();
-    return landed;
   };
   if (tid == 0) {
     tc::mbar_init(b_bar, 1);
-    tc::mbar_init(&a_full[0], 1);
-    tc::mbar_init(&a_full[1], 1);
-    tc::mbar_init(&mma_bar[0], 1);
-    tc::mbar_init(&mma_bar[1], 1);
+    tc::mbar_init(a_full, 1);
+    tc::mbar_init(mma_bar, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     if (!skipped) {
       const uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1) + (part - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
       tc::mbar_expect_tx(b_bar, PACK_BYTES);
       tc::bulk_load(smem + FIN_B, img, PACK_BYTES, b_bar);
-      load_a(blockIdx.x, 0);
-      if ((int)blockIdx.x + stride < n_pairs) load_a(blockIdx.x + stride, 1);
+      load_qt(blockIdx.x);
     }
   }
-  if (warp == 1) tc::tmem_alloc(tmem_slot, 256);
+  if (warp == 1) tc::tmem_alloc(tmem_slot, 128);
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  const int quarter = warp & 3, colq = warp >> 2;  // TMEM lane quarter (token rows) and column quarter of this warp
-  const int r = quarter * 32 + lane;
+  const int quarter = warp & 3, colq = warp >> 2;  // accumulator: TMEM lane quarter (token rows) and column quarter of this warp
+  const int hw = tid >> 4, sub = tid & 15;          // streaming pass: half-warp index (32 of them) and lane inside it
+  const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
+  float2 wv[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    wv[i] = a.norm_weight ? make_float2(a.norm_weight[8 * sub + 2 * i], a.norm_weight[8 * sub + 2 * i + 1]) : make_float2(1.f, 1.f);
   bool ok = true;
-  if (warp == 0 && !skipped) issue_pair(0, tm);
 
   int it = 0;
   for (int pair = blockIdx.x; pair < n_pairs && ok; pair += stride, ++it) {
-    const int stage = it & 1;
     const int c0 = c_begin + 2 * pair;
     const int64_t tok0 = sp.t0 + (int64_t)c0 * C;
     const int rows = min(min(2, c_end - c0) * C, sp.len - c0 * C);
-    const bool live = r < rows;
-    // the next pair's product runs while this pair is finished (its accumulator was drained an iteration ago)
-    if (warp == 0 && !skipped && pair + stride < n_pairs) issue_pair(it + 1, tm);
-    // rows this thread adds and gates
-    float x[32];
-    uint4 zraw[4];
-    if (!skipped && live) {
-      const float* ol = o_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + 32 * colq;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 v = *reinterpret_cast<const float4*>(ol + 4 * i);
-        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = 0.f;
-    }
-    if (a.z != nullptr) {
-      const __nv_bfloat16* zr = reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b + (tok0 + r) * a.z_stride_t +
-                                (int64_t)h * a.z_stride_h + 32 * colq;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) zraw[i] = live ? *reinterpret_cast<const uint4*>(zr + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
-    }
     if (!skipped) {
-      ok = tc::mbar_wait(&mma_bar[stage], (uint32_t)(it >> 1) & 1u, abort_flag);
-      tc::tc_fence_after_sync();
-      // this pair's images have been read: their stage takes the images of the pair after the next
-      if (ok && tid == 0 && pair + 2 * stride < n_pairs) load_a(pair + 2 * stride, stage);
-      if (ok) {
-        uint32_t acc[32];
-        tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 128u * (uint32_t)stage + 32 * colq, acc);
-        tc::tmem_ld_wait();
+      if (warp == 0) {
+        bool landed = it > 0 || tc::mbar_wait_warp(b_bar, 0, abort_flag);
+        landed = landed && tc::mbar_wait_warp(a_full, (uint32_t)it & 1u, abort_flag);
+        tc::tc_fence_after_sync();
+        if (landed && tc::elect_one()) {
+          constexpr uint32_t idesc = tc::idesc_f16(128, 128, 1, 1, true, false);  // A MN-major (token rows), B K-major
+          const uint32_t sa = tc::smem_u32(smem + FIN_A), sb = tc::smem_u32(smem + FIN_B);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] += __uint_as_float(acc[i]);
-      }
-    }
-    if (a.z != nullptr) {
-      const bool gate_first = (a.flags & AVE_GDN_FLAG_GATE_FIRST) != 0;
-      float gate[32];
+          for (int t = 0; t < 3; ++t) {  // hi hi, hi lo, lo hi
+            const uint32_t ab = sa + (t == 2 ? 32768u : 0u), bb = sb + (t == 1 ? 32768u : 0u);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t wds[4] = {zraw[i].x, zraw[i].y, zraw[i].z, zraw[i].w};
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          gate[8 * i + 2 * w] = silu(__uint_as_float(wds[w] << 16));
-          gate[8 * i + 2 * w + 1] = silu(__uint_as_float(wds[w] & 0xffff0000u));
+            for (int k = 0; k < 8; ++k)  // 16 d_k rows of qt^T per step: 2048 bytes; the two chunks' images lie 16384 bytes apart
+              tc::mma_ss(tm, tc::smem_desc_sw128(ab + k * 2048, 16384, 1024),
+                         tc::smem_desc_sw128(bb + (uint32_t)((k >> 2) * 16384 + (k & 3) * 32), 16, 1024), idesc, (t | k) != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(mma_bar);
         }
+        __syncwarp();
       }
-      float ss = 0.f;
+      ok = tc::mbar_wait(mma_bar, (uint32_t)it & 1u, abort_flag);
+      tc::tc_fence_after_sync();
+      // the images have been read: the next pair's take their place while this pair is finished
+      if (ok && tid == 0 && pair + stride < n_pairs) load_qt(pair + stride);
+      if (ok) {  // accumulator row -> staged row (this warp: 32 token rows x 32 columns)
+        uint32_t acc[32];
+        tc::tmem_ld32(tm + ((uint32_t)(quarter * 32) << 16) + 32 * colq, acc);
+        tc::tmem_ld_wait();
+        float* dstrow = stage + (quarter * 32 + lane) * FIN_PITCH + 32 * colq;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (gate_first) x[i] *= gate[i];
-        ss = fmaf(x[i], x[i], ss);
-      }
-      red[4 * r + colq] = ss;
-      __syncthreads();
-      const float4 s4 = *reinterpret_cast<const float4*>(red + 4 * r);
-      const float rinv = rsqrtf((s4.x + s4.y + s4.z + s4.w) * (1.0f / D) + a.norm_eps);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float wv = a.norm_weight ? a.norm_weight[32 * colq + i] : 1.0f;
-        x[i] *= rinv * wv * (gate_first ? 1.0f : gate[i]);
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(dstrow + 4 * i) = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
       }
     }
-    if (live && ok) {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (tok0 + r) * a.o_stride_t + (int64_t)h * a.o_stride_h +
-                           32 * colq;
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
-                                                            pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
-    }
-    // this pair's accumulator is free once every thread has read its part of the product
     tc::tc_fence_before_sync();
-    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;  // staged rows complete; the accumulator is free for the next product
     tc::tc_fence_after_sync();
+    if (ok) {
+      // streaming pass: this half-warp takes token rows hw, hw + 32, hw + 64, hw + 96
+      float2 x[4][4];
+      uint4 zraw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = hw + 32 * u;
+        const bool live = r < rows;
+        if (!skipped && live) {
+          const float* ol = o_f32 + (((int64_t)sp.b * a.T + tok0 + r) * a.Hv + h) * D + 8 * sub;
+          const float4 o0 = *reinterpret_cast<const float4*>(ol), o1 = *reinterpret_cast<const float4*>(ol + 4);
+          const float4 p0 = *reinterpret_cast<const float4*>(stage + r * FIN_PITCH + 8 * sub);
+          const float4 p1 = *reinterpret_cast<const float4*>(stage + r * FIN_PITCH + 8 * sub + 4);
+          x[u][0] = make_float2(o0.x + p0.x, o0.y + p0.y); x[u][1] = make_float2(o0.z + p0.z, o0.w + p0.w);
+          x[u][2] = make_float2(o1.x + p1.x, o1.y + p1.y); x[u][3] = make_float2(o1.z + p1.z, o1.w + p1.w);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[u][i] = make_float2(0.f, 0.f);
+        }
+        zraw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (a.z != nullptr && live)
+          zraw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.z) + sp.b * a.z_stride_b +
+                                                    (tok0 + r) * a.z_stride_t + (int64_t)h * a.z_stride_h + 8 * sub);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = hw + 32 * u;
+        uint32_t packed[4];
+        if (a.z != nullptr) {
+          float2 gate[4] = {silu2(bf16x2_to_float2(zraw[u].x)), silu2(bf16x2_to_float2(zraw[u].y)),
+                            silu2(bf16x2_to_float2(zraw[u].z)), silu2(bf16x2_to_float2(zraw[u].w))};
+          float2 ss2 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (gate_first) x[u][i] = __fmul2_rn(x[u][i], gate[i]);
+            ss2 = __ffma2_rn(x[u][i], x[u][i], ss2);
+          }
+          float ss = ss2.x + ss2.y;
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // stays inside the half-warp
+          const float rinv = rsqrtf(ss * (1.0f / D) + a.norm_eps);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 y2 = __fmul2_rn(__fmul2_rn(x[u][i], make_float2(rinv, rinv)), wv[i]);
+            if (!gate_first) y2 = __fmul2_rn(y2, gate[i]);
+            packed[i] = pack_bf16x2(y2.x, y2.y);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) packed[i] = pack_bf16x2(x[u][i].x, x[u][i].y);
+        }
+        if (r < rows)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (tok0 + r) * a.o_stride_t +
+                                    (int64_t)h * a.o_stride_h + 8 * sub) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+    __syncthreads();  // the staged rows have been read: the next pair may overwrite them
   }
   tc::tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u && tid == 0 && a.status != nullptr) atomicOr(a.status, AVE_GDN_DEV_WAIT_EXPIRED);
   if (warp == 1) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tm, 256);
+    tc::tmem_dealloc(tm, 128);
   }
 }
 
@@ -1439,7 +1445,10 @@ WsLayout ws_layout(const AveGdnArgs& a, bool plain) {
     const int64_t per_head = (NUM_SMS / (heads_total > 0 ? heads_total : 1) + 1) / 2;  // chains per head that still get an SM each: 2S - 1
     int S = per_head < MAX_PARTS ? (int)per_head : MAX_PARTS;
     while (S > 1 && max_chunks / S < 16) --S;
-    L.parts = max(S, 1);
+    // Two parts only halve the walk and pay for it with a third as many chains again plus the fix-up of half the rows:
+    // measured break-even (32 heads, 8192 tokens: 0.46 ms either way).  From three parts on the cut wins: 4 / 8 / 16 heads
+    // at 32768 tokens run 3.0x / 2.0x / 1.3x faster than the plain chain.
+    L.parts = S >= 3 ? S : 1;
   }
   L.part_begin[0] = 0;
   {
@@ -1634,6 +1643,7 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
     AVE_CUDA_TRY(cudaFuncSetAttribute(chunk_scan_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM));
     AVE_CUDA_TRY(cudaFuncSetAttribute(part_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FIN_SMEM));
+    AVE_CUDA_TRY(cudaFuncSetAttribute(part_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)COMBINE_SMEM));
     dev.attr_set = true;
   }
   if (a.cu_seqlens != nullptr) {
@@ -1662,11 +1672,11 @@ int launch_prefill_tc(const AveGdnArgs& a, cudaStream_t stream, bool plain) {
     if (beside) {
       AVE_CUDA_TRY(cudaEventRecord(scanned, s));
       AVE_CUDA_TRY(cudaStreamWaitEvent(side_stream, scanned, 0));
-      part_combine_kernel<<<cgrid, 256, 0, side_stream>>>(a, chunk_start, carry, m0_pack, plan);
+      part_combine_kernel<<<cgrid, 256, COMBINE_SMEM, side_stream>>>(a, chunk_start, carry, m0_pack, plan);
       AVE_CUDA_TRY(cudaGetLastError());
       AVE_CUDA_TRY(cudaEventRecord(combined, side_stream));
     } else {
-      part_combine_kernel<<<cgrid, 256, 0, s>>>(a, chunk_start, carry, m0_pack, plan);
+      part_combine_kernel<<<cgrid, 256, COMBINE_SMEM, s>>>(a, chunk_start, carry, m0_pack, plan);
       AVE_CUDA_TRY(cudaGetLastError());
     }
     int part_len = 0;  // the longest of the later parts

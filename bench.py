@@ -321,6 +321,26 @@ def bench_decode(steps=1000, warmup=20):
     return us, state_bytes, state_bytes + other, layer
 
 
+def bench_backward(steps=2):
+    """The backward pass on the headline shape (B=1, T=8192, 32 value heads): the correct-first reverse sweep, timed so
+    that its distance from the forward pass is on record."""
+    from avelang_b200 import gdn, synth
+    g = synth.config1().to("cuda")
+    d_o = torch.randn_like(g.v)
+    run = lambda: gdn.gated_delta_rule_backward(g.q, g.k, g.v, g.g, g.beta, d_o)
+    run()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    return {"metric": "gdn_backward_tokens_per_s", "value": T_PREFILL / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
+            "config": {"workload": "gradients of the headline prefill (no fused norm): token-by-token reverse sweep in fp32"}}
+
+
 def cpu_baseline(sample_tokens=T_PREFILL, reps=None, budget_s=12.0, n_seqs=1):
     """The C restatement of the token recurrence (fp32, OpenMP over sequence x head) on the host cores; repeated
     until about `budget_s` seconds of CPU work have been timed (or `reps` runs).  `n_seqs` sequences per run (the
@@ -703,6 +723,8 @@ def main():
                                        "peak_source": peaks["source"]}}
     if world > 1:
         barrier(world)
+    if rank == 0 and world == 1 and not args.no_decode:
+        line["backward"] = bench_backward()
     if rank == 0 and not args.no_cpu and world == 1:
         line["cpu_baseline"] = cpu_baseline()
     if not args.no_sharded:
