@@ -1161,11 +1161,12 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
     for (int e = tid; e < D * COMBINE_COLS; e += 256) cur[0][e / COMBINE_COLS][e % COMBINE_COLS] = src[(e / COMBINE_COLS) * D + cb * COMBINE_COLS + e % COMBINE_COLS];
   }
   // a thread fetches 16 float4 of the 128x128 tile: element 4 * (tid + 256 i), i.e. row (tid + 256 i) / 32
-  float4 pre[16];
+  float4 pre[16], psi_pre;
   auto fetch = [&](int p) {
     const float4* F4 = reinterpret_cast<const float4*>(tile_of(2 * p));
 #pragma unroll
     for (int i = 0; i < 16; ++i) pre[i] = F4[tid + 256 * i];
+    psi_pre = *reinterpret_cast<const float4*>(tile_of(2 * p - 1) + (int64_t)(tid >> 1) * D + cb * COMBINE_COLS + (tid & 1) * 4);
   };
   fetch(1);
   int b = 0;
@@ -1177,12 +1178,12 @@ part_combine_kernel(const AveGdnArgs a, const int32_t* __restrict__ chunk_start,
       float* dst = Fs + row * COMBINE_PITCH + c0;
       dst[0] = pre[i].x; dst[1] = pre[i].y; dst[2] = pre[i].z; dst[3] = pre[i].w;
     }
+    const float4 psi = psi_pre;
     if (p + 1 < active) fetch(p + 1);
     __syncthreads();
     {  // next = F_p cur + Psi_p: a thread owns one row k and four columns
       const int k = tid >> 1, j0 = (tid & 1) * 4;
       const float* Frow = Fs + k * COMBINE_PITCH;
-      const float4 psi = *reinterpret_cast<const float4*>(tile_of(2 * p - 1) + (int64_t)k * D + cb * COMBINE_COLS + j0);
       float acc0 = psi.x, acc1 = psi.y, acc2 = psi.z, acc3 = psi.w;
 #pragma unroll 16
       for (int d = 0; d < D; ++d) {

@@ -626,6 +626,12 @@ def profile_case(name: str):
         for _ in range(2):
             gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, initial_state=inp.initial_state,
                                        output_final_state=True, cu_seqlens=inp.cu_seqlens)
+    elif name == "parts8k":
+        # few long chains: one sequence of 8192 tokens x 4 value heads is cut into parallel parts (transition chains,
+        # combine, fix-up); about 0.1 GB of scratch
+        inp = synth.config1(T=8192, Hk=2, Hv=4).to("cuda")
+        for _ in range(3):
+            gdn.chunk_gated_delta_rule(inp.q, inp.k, inp.v, inp.g, inp.beta, output_final_state=True, z=inp.z)
     elif name == "gemm1544":
         # the in-projection of one rank of eight at an eighth of the rows (16384 x 1544 x 2048): ragged last column tile
         from avelang_b200 import gemm
@@ -661,7 +667,7 @@ def main():
     ap.add_argument("--workload", default="prefill", choices=["prefill", "varlen", "block", "helpers"],
                     help="prefill (default, the headline line), varlen (head-sharded packed prefill), block, or helpers "
                          "(GEMM, conv1d, norm and gate kernels timed alone on one GPU)")
-    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k", "gemm1544", "conv", "norm"],
+    ap.add_argument("--profile-case", default=None, choices=["decode", "prefill2048", "varlen32k", "parts8k", "gemm1544", "conv", "norm"],
                     help="run a small fixed case for a profiler capture and exit")
     args = ap.parse_args()
     if args.profile_case:
@@ -718,7 +724,7 @@ def main():
                           "roofline": {"bound": "hbm", "achieved": all_bytes / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": all_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
                                        "frac_of_nominal_8TBps": all_bytes / (us * 1e-6) / 8e12,
-                                       "traffic": 1_020_755_968,  # dram read+write per launch, ncu capture at full size
+                                       "traffic": 1_021_515_264,  # dram read + write of one launch, ncu capture at full size
                                        "traffic_source": "profiles/decode_gdn_decode_kernel_config2.md",
                                        "peak_source": peaks["source"]}}
     if world > 1:

@@ -18,6 +18,11 @@
  *  - Strides are in ELEMENTS.  The innermost (head-feature) dimension must be contiguous and every row
  *    16-byte aligned.
  *  - Return value: AVE_GDN_OK or an AveGdnStatus code.  Nothing aborts or throws across the boundary.
+ *  - Thread safety: every entry point may be called from several host threads at once.  The prefill enqueues under a
+ *    per-device mutex (its schedule forks onto library-owned helper streams through events, and the record/wait pairs
+ *    of two callers must not interleave); a small pool of helper-stream sets per device, picked by the caller's stream,
+ *    lets prefills on different streams overlap on the GPU.  Calls that overlap on the GPU need their own scratch and
+ *    outputs.
  *  - Data-dependent faults (a slot index outside the pool, a bounded device wait that ran out) cannot be
  *    seen by the host without a sync: the kernels skip the offending unit and OR a bit into the optional
  *    device word `status` (see AVE_GDN_DEV_*).
@@ -48,7 +53,8 @@ typedef enum AveGdnStatus {
 
 /* bits OR-ed into the device status word */
 #define AVE_GDN_DEV_BAD_SLOT 1u      /* state index >= num_slots: that sequence was skipped */
-#define AVE_GDN_DEV_BAD_SEQLEN 2u    /* cu_seqlens not monotone or beyond T: that sequence was skipped */
+#define AVE_GDN_DEV_BAD_SEQLEN 2u    /* cu_seqlens not monotone inside [0, T]: the whole batch was skipped (its outputs are
+                                        undefined); or a sequence longer than max_seqlen: that sequence was skipped */
 #define AVE_GDN_DEV_WAIT_EXPIRED 4u  /* a bounded wait inside a kernel gave up */
 
 /* flags */
@@ -110,8 +116,10 @@ int ave_gdn_prefill_launch_count(const AveGdnArgs* args);
  * that has handed all of HBM to its paged pools, a plug-in callback limited to pre-registered buffers, a path where
  * allocator calls are forbidden): `workspace` / `workspace_bytes` are ignored and the scratch is a fixed 64 MiB
  * array inside the library (AVE_GDN_NOALLOC_SCRATCH_BYTES), held by every GPU that loads the library until the
- * process exits.  Requests needing more scratch than that, i.e. more than about 1000 (chunk, value head) pairs, return
- * AVE_GDN_WORKSPACE_TOO_SMALL; only dk = dv = 128 is served.  Calls no cudaMalloc/cudaFree or other allocating routine.
+ * process exits.  Requests needing more scratch than that, i.e. more than about 1000 (chunk, value head) pairs without
+ * a gate tensor z and about 670 with one (the un-normalised fp32 output then waits in the array too), return
+ * AVE_GDN_WORKSPACE_TOO_SMALL; only dk = dv = 128 is served.  The call runs the plain schedule: one launch per pass on
+ * the caller's stream, no helper streams or events.  Calls no cudaMalloc/cudaFree or other allocating routine.
  * The first call on a device looks up the array's device address and should be made outside stream capture.  All
  * calls share the one array: calls that overlap on the GPU (different streams) race; nothing needs clearing between
  * calls.  This entry point has no counterpart in the reference. */
