@@ -723,12 +723,10 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   const int hk = h / (a.Hv / a.Hk);
   if (a.cu_seqlens != nullptr && chunk_start[a.n_seqs] < 0) return;  // the chunk table was rejected: nothing runs
   SeqSpan sp = seq_span(a.cu_seqlens, n, a.T, a.status);
-  if (a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen) {
-    // longer than the caller's bound: the launch schedule was sized from that bound, so the sequence is skipped and
-    // flagged like a malformed cu_seqlens entry
-    if (a.status != nullptr && threadIdx.x == 0) atomicOr(a.status, AVE_GDN_DEV_BAD_SEQLEN);
-    sp.ok = false; sp.len = 0;
-  }
+  // longer than the caller's bound: the launch schedule was sized from that bound, so the sequence is skipped (zero
+  // output, no state access, like a negative slot) and flagged
+  const bool too_long = a.cu_seqlens != nullptr && a.max_seqlen > 0 && sp.len > a.max_seqlen;
+  if (too_long && a.status != nullptr && threadIdx.x == 0) atomicOr(a.status, AVE_GDN_DEV_BAD_SEQLEN);
   if (!sp.ok || sp.len == 0) {
     if (plan.r0 > 0 || chain > 0) return;
     // zero-length sequence: the final state is the initial state
@@ -744,7 +742,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   }
   const int seq_chunks = (sp.len + C - 1) / C;
   // a sequence that ends inside part 0 is one plain chain: outputs and the final state leave directly
-  const bool multi = kMulti && plan.parts > 1 && seq_chunks > plan.part_begin[1];
+  const bool multi = kMulti && plan.parts > 1 && seq_chunks > plan.part_begin[1] && !too_long;
   if (chain > 0 && (!multi || plan.part_begin[part] >= seq_chunks)) return;
   int slot = n;
   if (a.state_indices != nullptr) {
@@ -754,6 +752,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       slot = -1;
     }
   }
+  if (too_long) slot = -1;
   __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(a.o) + sp.b * a.o_stride_b + (int64_t)h * a.o_stride_h;
   // where this chain's per-token rows go: the local rows of later parts wait in fp32 scratch for the fix-up; part 0
   // writes fp32 scratch only when a gated norm follows, else the result itself; the transition chain's rows leave as

@@ -54,7 +54,8 @@ typedef enum AveGdnStatus {
 /* bits OR-ed into the device status word */
 #define AVE_GDN_DEV_BAD_SLOT 1u      /* state index >= num_slots: that sequence was skipped */
 #define AVE_GDN_DEV_BAD_SEQLEN 2u    /* cu_seqlens not monotone inside [0, T]: the whole batch was skipped (its outputs are
-                                        undefined); or a sequence longer than max_seqlen: that sequence was skipped */
+                                        undefined); or a sequence longer than max_seqlen: that sequence was skipped like
+                                        one with a negative slot (zero output, state untouched) */
 #define AVE_GDN_DEV_WAIT_EXPIRED 4u  /* a bounded wait inside a kernel gave up */
 
 /* flags */
@@ -86,8 +87,8 @@ typedef struct AveGdnArgs {
   int32_t num_slots; /* tiles in the state arrays; n_seqs when state_indices is null */
   int32_t chunk;     /* prefill: 64 */
   int32_t max_seqlen; /* optional, with cu_seqlens: an upper bound of the longest sequence in tokens (0 = unknown).  It
-                         sizes the launch schedule of the prefill; a sequence longer than it is skipped and flagged
-                         AVE_GDN_DEV_BAD_SEQLEN. */
+                         sizes the launch schedule of the prefill; a sequence longer than it is skipped (zero output,
+                         state untouched) and flagged AVE_GDN_DEV_BAD_SEQLEN. */
   int64_t q_stride_b, q_stride_t, q_stride_h;
   int64_t k_stride_b, k_stride_t, k_stride_h;
   int64_t v_stride_b, v_stride_t, v_stride_h;
