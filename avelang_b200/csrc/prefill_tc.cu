@@ -12,8 +12,9 @@
 //     O^T  = qs-scaled H Q^T + Vn^T P^T   (A = H or Vn hi/lo from TMEM, B = Q or P hi/lo, K-major)
 //     H   <- e^{b_C} H + Vd^T K           (A = Vd hi/lo from TMEM, B = K, MN-major), Vd_j = e^{b_C-b_j} Vn_j
 //   The fp32 master copy of H lives in the chain-epilogue threads' registers; its bf16 hi/lo image is rewritten to
-//   TMEM every chunk.  Four warpgroups with redistributed register budgets: control (warp 0 = TMA loader, warp 1 = MMA
-//   issuer), two chain-epilogue groups (each covers all 128 TMEM lanes and half of the columns), one output group.
+//   TMEM every chunk.  Four warpgroups with redistributed register budgets: control (warp 0 = TMA loader, warp 1 issues
+//   the MMAs the recurrence waits for, warp 2 the output MMAs), two chain-epilogue groups (each covers all 128 TMEM
+//   lanes and half of the columns), one output group.
 //   With a gate tensor z the un-normalised output goes to fp32 scratch and a gated-RMSNorm launch finishes it
 //   (optionally storing each row into every GPU's buffer: the fused all-gather).
 // All waits are bounded; on give-up the CTA drains, frees its tensor memory and sets a status bit.
@@ -138,12 +139,6 @@ constexpr int QT_BYTES = 2 * 128 * 64 * 2;     // bf16 hi image | lo image of on
 // two 64-wide K halves of 128-byte rows with the 128-byte swizzle (the layout tcgen05.mma reads)
 __device__ __forceinline__ uint32_t kmajor_piece_off(int row, int k8) {
   return (uint32_t)((k8 >> 3) * 16384 + row * 128 + (((k8 & 7) ^ (row & 7)) << 4));
-}
-__device__ __forceinline__ int part_of(const ScanPlan& pl, int cis) {
-  int p = 0;
-#pragma unroll
-  for (int i = 1; i < MAX_PARTS; ++i) p += (i < pl.parts && cis >= pl.part_begin[i]) ? 1 : 0;
-  return p;
 }
 
 // ------------------------------------------------------------------------------------------------ pass 1
@@ -635,15 +630,22 @@ chunk_prep_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, cons
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
-constexpr int SCAN_THREADS = 512;   // warpgroup 0: warp 0 loader, warp 1 MMA issuer; warpgroups 1,2: chain epilogue (two
-                                    // column groups); warpgroup 3: output.  Launch allocation is 128 registers per thread,
-                                    // redistributed below as 72 / 176 / 176 / 88 (sum 512).
-constexpr int REGS_CTRL = 72, REGS_CHAIN = 176, REGS_OUT = 88;
-static_assert(REGS_CTRL + 2 * REGS_CHAIN + REGS_OUT <= 4 * 128, "register redistribution exceeds the launch allocation");
+// Warpgroup 0: warp 0 loader, warps 1 and 2 MMA issuers; warpgroups 1..NG: chain epilogue, each covering all 128 TMEM
+// lanes and 1/NG of the columns; the last warpgroup: output.  (Four epilogue groups at 80 registers were measured: no
+// faster, the epilogue is bound by the instructions issued per scheduler, not by the work per thread.)
+constexpr int NG = 2;
+constexpr int SCAN_THREADS = 32 * (4 + 4 * NG + 4);
+constexpr int REGS_LAUNCH = 128;
+constexpr int REGS_CTRL = 72, REGS_CHAIN = 168, REGS_OUT = 104;
+static_assert(NG == 2, "the register split below is for two epilogue groups");
+static_assert(REGS_CTRL + NG * REGS_CHAIN + REGS_OUT <= (NG + 2) * REGS_LAUNCH, "register redistribution exceeds the launch allocation");
+static_assert(SCAN_THREADS * REGS_LAUNCH <= 65536, "launch allocation exceeds the register file");
+constexpr int HC = D / NG;   // columns of H (d_k) per chain-epilogue group
+constexpr int VC = C / NG;   // columns of Vn (tokens) per group
 constexpr int ST_WHI = 0, ST_WLO = 16384, ST_Q = 32768, ST_K = 49152, ST_PHI = 65536, ST_PLO = 73728, ST_V = 81920;
 constexpr int STAGE = 98304;                         // multiple of 1024
 constexpr int SCAL_BYTES = SCAL_FLOATS * 4;
-constexpr uint32_t STAGE_TX = STAGE + SCAL_BYTES;
+constexpr uint32_t TILES_TX = STAGE - 2 * REC_P;  // W hi, W lo, Q, K, V
 constexpr int OFF_SCAL = 2 * STAGE;                  // 4 x [qs | ks | decay]: a deeper ring than the tile stages, because
                                                      // the output warps read qs up to a chunk after the stage is recycled
 constexpr int OFF_VT = OFF_SCAL + 4 * SCAL_BYTES;    // single buffer: Tu hi | Tu lo (they come from scratch that pass 1 has
@@ -654,17 +656,15 @@ static_assert(OFF_VT % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 constexpr int OFF_BARS = OFF_VT + VT_BYTES;
 constexpr size_t SCAN_SMEM = OFF_BARS + 256 + 1024;
 // TMEM columns
-constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 128, TM_VNLO = 160, TM_VDHI = 192, TM_VDLO = 224,
-                   TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
-
-
-// Barrier among a group of warps built on an mbarrier so that, unlike bar.sync, the wait is bounded.
-__device__ __forceinline__ bool group_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag) {
-  __syncwarp();
-  if (lane == 0) tc::mbar_arrive(bar);
-  const bool ok = tc::mbar_wait_warp(bar, phase, abort_flag);
-  phase ^= 1u;
-  return ok;
+constexpr uint32_t TM_HHI = 0, TM_HLO = 64, TM_VN = 128, TM_VNHI = 192, TM_VNLO = 224, TM_O1 = 256, TM_O2 = 320, TM_DH = 384;
+// The bf16 hi and lo images of Vd reuse the Vn accumulator's columns.  Each chain-epilogue group packs its VC tokens
+// into its own VC columns (hi in the first half, lo in the second), so a warp overwrites only columns it has itself
+// read and the groups need no barrier between reading the accumulator and writing the images.  Their only reader is
+// the state-increment MMA, issued by the same thread that next writes the accumulator (U^T of the following chunk),
+// so program order protects them.  (The images of Vn, read by the other issuer's O2, have columns of their own.)
+// 16-token K step k of the Vd image starts at:
+__host__ __device__ constexpr uint32_t vd_img_col(int k, bool lo) {
+  return TM_VN + (uint32_t)(VC * ((16 * k) / VC) + ((16 * k) % VC) / 2 + (lo ? VC / 2 : 0));
 }
 
 // Issues `ksteps` MMAs D (+)= A[tmem] * B[smem] over consecutive 16-wide K steps.  A advances 8 TMEM columns per
@@ -695,18 +695,24 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
-  uint64_t* full = bars;          // [2] stage landed
-  uint64_t* empty = bars + 2;     // [2] stage consumed
+  uint64_t* full = bars;          // [2] W, Q, K and V tiles of the stage landed
+  uint64_t* pfull = bars + 2;     // [2] P tiles and the scale vectors of the stage landed
   uint64_t* h_ready = bars + 4;   // bf16 image of the state is in TMEM
   uint64_t* vn_full = bars + 5;   // -(H W^T) accumulated
   uint64_t* vn_ready = bars + 6;  // Vn / Vd hi+lo written back to TMEM
   uint64_t* dh_full = bars + 7;   // state increment accumulated
   uint64_t* o_full = bars + 8;    // both output accumulators complete
-  uint64_t* o_empty = bars + 9;   // output accumulators drained
+  uint64_t* o1_empty = bars + 9;  // O1 accumulator drained (the output warps take it first, whole, so O1 of the next chunk can run early)
+  uint64_t* o2_empty = bars + 12; // O2 accumulator drained
+  uint64_t* o1_done = bars + 13;  // O1 complete: the bf16 image of H may be overwritten
   uint64_t* u_full = bars + 10;   // Tu tiles landed
   uint64_t* u_empty = bars + 11;  // the U^T MMAs that read them are complete
-  uint64_t* chain_bar = bars + 12;
   uint64_t* vd_ready = bars + 14; // Vd hi+lo written to TMEM (the state update needs nothing else)
+  // a stage is given back tile by tile, as soon as the last MMA that reads the tile is complete
+  uint64_t* w_empty = bars + 16;  // [2] after the Vn MMAs
+  uint64_t* q_empty = bars + 18;  // [2] after O1
+  uint64_t* k_empty = bars + 20;  // [2] after the state increment
+  uint64_t* p_empty = bars + 22;  // [2] after O2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -784,11 +790,12 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&full[0], 1); tc::mbar_init(&full[1], 1);
-    tc::mbar_init(&empty[0], 9); tc::mbar_init(&empty[1], 9);
-    tc::mbar_init(h_ready, 8); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 8);
-    tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o_empty, 4);
+    tc::mbar_init(&pfull[0], 1); tc::mbar_init(&pfull[1], 1);
+    for (int i = 0; i < 2; ++i) { tc::mbar_init(&w_empty[i], 1); tc::mbar_init(&q_empty[i], 1); tc::mbar_init(&k_empty[i], 1); tc::mbar_init(&p_empty[i], 1); }
+    tc::mbar_init(h_ready, 4 * NG); tc::mbar_init(vn_full, 1); tc::mbar_init(vn_ready, 4 * NG);
+    tc::mbar_init(dh_full, 1); tc::mbar_init(o_full, 1); tc::mbar_init(o1_empty, 4); tc::mbar_init(o2_empty, 4); tc::mbar_init(o1_done, 1);
     tc::mbar_init(u_full, 1); tc::mbar_init(u_empty, 1);
-    tc::mbar_init(chain_bar, 8); tc::mbar_init(vd_ready, 8);
+    tc::mbar_init(vd_ready, 4 * NG);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -799,31 +806,42 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
   const uint32_t tm = *tmem_slot;
 
   if (warp < 4) {
-  tc::reg_set<REGS_CTRL, 128>();
+  tc::reg_set<REGS_CTRL, REGS_LAUNCH>();
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
+    // Two stages of {W hi, W lo, Q, K, P hi, P lo, V}.  A tile of chunk c+2 is fetched as soon as the last MMA that
+    // reads the same tile of chunk c is complete (W after the Vn MMAs, early in the chunk's period; P last), so most of a
+    // stage lands more than a period before it is needed instead of a fraction of one.
     if (lane == 0) {
       for (int c = 0; c < n_chunks; ++c) {
         const int s = c & 1;
-        const uint32_t u = (uint32_t)(c >> 1);
-        if (!tc::mbar_wait(&empty[s], (u & 1u) ^ 1u, abort_flag)) break;
+        const uint32_t free_par = ((uint32_t)(c >> 1) & 1u) ^ 1u;  // parity of "chunk c-2 is done with it"
         uint8_t* st = smem + s * STAGE;
         const int64_t rec = (int64_t)(c_first + c) * a.Hv + h;
         const int tok = sp.t0 + c * C;
-        tc::mbar_expect_tx(&full[s], phi ? STAGE_TX - 16384u : STAGE_TX);  // the transition chain has no V
-        tc::bulk_load(st + ST_WHI, w_hi_ws + rec * (C * D), REC_W, &full[s]);  // W^T tile images: 128 d_k rows of 64 tokens
-        tc::bulk_load(st + ST_WLO, w_lo_ws + rec * (C * D), REC_W, &full[s]);
-        tc::tma_load_4d(st + ST_Q, &maps.q, &full[s], 0, hk, tok, sp.b);
-        tc::tma_load_4d(st + ST_Q + 8192, &maps.q, &full[s], 64, hk, tok, sp.b);
-        tc::tma_load_4d(st + ST_K, &maps.k, &full[s], 0, hk, tok, sp.b);
-        tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
-        tc::bulk_load(st + ST_PHI, p_hi_ws + rec * (C * C), REC_P, &full[s]);
-        tc::bulk_load(st + ST_PLO, p_lo_ws + rec * (C * C), REC_P, &full[s]);
+        // The Vn MMAs of chunk c-2 are complete: so are its U^T MMAs, issued before them (W and V slots are free), and
+        // the MMA warp has long passed its wait for the stage's previous phase, so the barrier can be armed again.
+        if (!tc::mbar_wait(&w_empty[s], free_par, abort_flag)) break;
+        tc::mbar_expect_tx(&full[s], phi ? TILES_TX - 16384u : TILES_TX);  // the transition chain has no V
         if (!phi) {
           tc::tma_load_4d(st + ST_V, &maps.v, &full[s], 0, h, tok, sp.b);
           tc::tma_load_4d(st + ST_V + 8192, &maps.v, &full[s], 64, h, tok, sp.b);
         }
-        tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &full[s]);
+        tc::bulk_load(st + ST_WHI, w_hi_ws + rec * (C * D), REC_W, &full[s]);  // W^T tile images: 128 d_k rows of 64 tokens
+        tc::bulk_load(st + ST_WLO, w_lo_ws + rec * (C * D), REC_W, &full[s]);
+        if (!tc::mbar_wait(&q_empty[s], free_par, abort_flag)) break;
+        tc::tma_load_4d(st + ST_Q, &maps.q, &full[s], 0, hk, tok, sp.b);
+        tc::tma_load_4d(st + ST_Q + 8192, &maps.q, &full[s], 64, hk, tok, sp.b);
+        if (!tc::mbar_wait(&k_empty[s], free_par, abort_flag)) break;
+        tc::tma_load_4d(st + ST_K, &maps.k, &full[s], 0, hk, tok, sp.b);
+        tc::tma_load_4d(st + ST_K + 8192, &maps.k, &full[s], 64, hk, tok, sp.b);
+        // P and the scale vectors last.  The scale-vector ring is four deep: the output warps read qs of chunk c-4 until
+        // they release its accumulators, which O1 of chunk c-2, and so this wait, comes after.
+        if (!tc::mbar_wait(&p_empty[s], free_par, abort_flag)) break;
+        tc::mbar_expect_tx(&pfull[s], 2 * REC_P + SCAL_BYTES);
+        tc::bulk_load(st + ST_PHI, p_hi_ws + rec * (C * C), REC_P, &pfull[s]);
+        tc::bulk_load(st + ST_PLO, p_lo_ws + rec * (C * C), REC_P, &pfull[s]);
+        tc::bulk_load(smem + OFF_SCAL + (c & 3) * SCAL_BYTES, scal_ws + rec * SCAL_FLOATS, SCAL_BYTES, &pfull[s]);
         if (phi) continue;
         // Tu of chunk c replaces that of chunk c-1 once the U^T MMAs of chunk c-1 have read it
         if (!tc::mbar_wait(u_empty, ((uint32_t)c & 1u) ^ 1u, abort_flag)) break;
@@ -834,22 +852,21 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (whole warp runs the loop,
-    // one elected lane issues)
+    // ------------------------------------------------------------------ chain MMA issuer (whole warp runs the loop, one
+    // elected lane issues): the MMAs the recurrence waits for.  One thread needs 20 to 60 cycles per MMA instruction, so
+    // the 68 instructions of a chunk are shared between two warps; this one keeps the state-dependent ones short:
+    //   U^T(c+1) -> [state published] Vn^T(c) -> [Vd written] dH(c)
     constexpr uint32_t id_vn = tc::idesc_f16(128, 64, 1, 1, false, true, true, false);    // negated A, B = W^T read MN-major
-    constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
     constexpr uint32_t id_dh = tc::idesc_f16(128, 128, 1, 1, false, true);                // B MN-major
     constexpr uint32_t id_u = tc::idesc_f16(128, 64, 1, 1, true, false);                  // A = V tile read MN-major
     const uint32_t vtb = tc::smem_u32(smem + OFF_VT);
     // U^T = V^T (Tu_hi + Tu_lo)^T opens the Vn^T accumulator of a chunk.  It does not depend on the state, so it is
-    // issued a chunk ahead, right behind the previous chunk's O2 MMAs (which read the same columns and, issued earlier
-    // by this thread, complete first): the tensor pipe runs it while the chain epilogue re-packs H.
-    auto issue_u = [&](int c) -> bool {
+    // issued a chunk ahead, right behind the previous chunk's state-increment MMAs (which read the Vd images in the
+    // same columns and, issued earlier by this thread, complete first): the tensor pipe runs it while the chain
+    // epilogue re-packs H.
+    auto issue_u = [&](int c) {
+      if (phi) return;  // v = 0: U^T = 0, the first Vn MMA overwrites the accumulator instead
       const uint32_t vb = tc::smem_u32(smem + (c & 1) * STAGE + ST_V);
-      if (!tc::mbar_wait_warp(&full[c & 1], (uint32_t)(c >> 1) & 1u, abort_flag)) return false;  // the V tile rides in the stage
-      if (phi) return true;  // v = 0: U^T = 0, the first Vn MMA below overwrites the accumulator instead
-      if (!tc::mbar_wait_warp(u_full, (uint32_t)c & 1u, abort_flag)) return false;
-      tc::tc_fence_after_sync();
       if (tc::elect_one()) {
 #pragma unroll
         for (int t = 0; t < 2; ++t)
@@ -860,13 +877,13 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         tc::mma_commit(u_empty);
       }
       __syncwarp();
-      return true;
     };
-    bool issuing = n_chunks > 0 && issue_u(0);
+    bool issuing = n_chunks > 0 && tc::mbar_wait_warp(&full[0], 0u, abort_flag) && (phi || tc::mbar_wait_warp(u_full, 0u, abort_flag));
+    if (issuing) { tc::tc_fence_after_sync(); issue_u(0); }
     for (int c = 0; c < n_chunks && issuing; ++c) {
       const int s = c & 1;
-      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
-      const uint32_t sb = tc::smem_u32(smem + s * STAGE);  // the stage has landed: issue_u(c) waited for it
+      const uint32_t cp = (uint32_t)c & 1u;
+      const uint32_t sb = tc::smem_u32(smem + s * STAGE);  // W, K have landed: this warp waited for the stage a chunk ago
       if (!tc::mbar_wait_warp(h_ready, cp, abort_flag)) break;
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
@@ -875,26 +892,50 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         issue_ts(tm + TM_VN, tm + TM_HHI, sb + ST_WLO, 2048, 0, 16, id_vn, 8, true);
         issue_ts(tm + TM_VN, tm + TM_HLO, sb + ST_WHI, 2048, 0, 16, id_vn, 8, true);
         tc::mma_commit(vn_full);
-      }
-      __syncwarp();
-      if (!tc::mbar_wait_warp(o_empty, cp ^ 1u, abort_flag)) break;
-      tc::tc_fence_after_sync();
-      if (tc::elect_one()) {
-        // O1 = (Hhi + Hlo) Q^T
-        issue_ts(tm + TM_O1, tm + TM_HHI, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, false);
-        issue_ts(tm + TM_O1, tm + TM_HLO, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, true);
+        tc::mma_commit(&w_empty[s]);
       }
       __syncwarp();
       if (!tc::mbar_wait_warp(vd_ready, cp, abort_flag)) break;
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // dH = (Vd_hi + Vd_lo) contracted with K over the chunk's tokens (K tile read MN-major: 16 token rows per step)
-        issue_ts(tm + TM_DH, tm + TM_VDHI, sb + ST_K, 2048, 0, 8192, id_dh, 4, false);
-        issue_ts(tm + TM_DH, tm + TM_VDLO, sb + ST_K, 2048, 0, 8192, id_dh, 4, true);
+        const uint64_t k_desc = tc::smem_desc_sw128(sb + ST_K, 8192, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc::mma_ts(tm + TM_DH, tm + vd_img_col(k, false), k_desc + (uint64_t)(128 * k), id_dh, k != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc::mma_ts(tm + TM_DH, tm + vd_img_col(k, true), k_desc + (uint64_t)(128 * k), id_dh, 1u);
         tc::mma_commit(dh_full);
+        tc::mma_commit(&k_empty[s]);
       }
       __syncwarp();
-      if (!tc::mbar_wait_warp(vn_ready, cp, abort_flag)) break;
+      if (c + 1 < n_chunks) {
+        // the next chunk's tiles, polled together so that the latencies of phases that are already complete overlap
+        uint64_t* b_f = &full[(c + 1) & 1];
+        const uint32_t p_f = (uint32_t)((c + 1) >> 1) & 1u;
+        if (!(phi ? tc::mbar_wait_warp(b_f, p_f, abort_flag) : tc::mbar_wait2(b_f, p_f, u_full, (uint32_t)(c + 1) & 1u, abort_flag))) break;
+        tc::tc_fence_after_sync();
+        issue_u(c + 1);
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ output MMA issuer: O1 = H Q^T once the Vn MMAs are
+    // complete (so that it runs behind them, while the chain epilogue converts Vn), O2 = Vn P^T once Vn hi/lo are back
+    constexpr uint32_t id_n64 = tc::idesc_f16(128, 64, 1, 1, false, false);
+    for (int c = 0; c < n_chunks; ++c) {
+      const int s = c & 1;
+      const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
+      const uint32_t sb = tc::smem_u32(smem + s * STAGE);
+      if (!tc::mbar_wait3(vn_full, cp, o1_empty, cp ^ 1u, &full[s], u & 1u, abort_flag)) break;
+      tc::tc_fence_after_sync();
+      if (tc::elect_one()) {
+        // O1 = (Hhi + Hlo) Q^T; the chain epilogue waits for its completion before it overwrites the bf16 image of H
+        issue_ts(tm + TM_O1, tm + TM_HHI, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, false);
+        issue_ts(tm + TM_O1, tm + TM_HLO, sb + ST_Q, 32, 8192 - 128, 16, id_n64, 8, true);
+        tc::mma_commit(o1_done);
+        tc::mma_commit(&q_empty[s]);
+      }
+      __syncwarp();
+      if (!tc::mbar_wait3(vn_ready, cp, o2_empty, cp ^ 1u, &pfull[s], u & 1u, abort_flag)) break;
       tc::tc_fence_after_sync();
       if (tc::elect_one()) {
         // O2 = Vn_hi Phi^T + Vn_lo Phi^T + Vn_hi Plo^T
@@ -902,48 +943,46 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
         issue_ts(tm + TM_O2, tm + TM_VNLO, sb + ST_PHI, 32, 0, 16, id_n64, 4, true);
         issue_ts(tm + TM_O2, tm + TM_VNHI, sb + ST_PLO, 32, 0, 16, id_n64, 4, true);
         tc::mma_commit(o_full);
-        tc::mma_commit(&empty[s]);
+        tc::mma_commit(&p_empty[s]);
       }
       __syncwarp();
-      if (c + 1 < n_chunks) issuing = issue_u(c + 1);
     }
   }
-  } else if (warp < 12) {
-    tc::reg_set<REGS_CHAIN, 128>();
+  } else if (warp < 4 + 4 * NG) {
+    tc::reg_set<REGS_CHAIN, REGS_LAUNCH>();
     // ------------------------------------------------------------------ chain epilogue: Vn/Vd conversion and state update
-    const int grp = (warp - 4) >> 2;    // column half
+    const int grp = (warp - 4) >> 2;    // column group
     const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
     const int d = quarter * 32 + lane;  // row of H (d_v index)
     const uint32_t lane_addr = tm + ((uint32_t)(quarter * 32) << 16);
     const int64_t tile = ((int64_t)slot * a.Hv + h) * (int64_t)(D * D);
     bool alive = true;
-    uint32_t sync_phase = 0;
 
-    float2 Hreg[32];  // H[d][64*grp + 2w .. +1] = M[64*grp + 2w .. +1][d]
+    float2 Hreg[HC / 2];  // H[d][HC*grp + 2w .. +1] = M[HC*grp + 2w .. +1][d]
     // first launch of a chain: part 0 starts from the caller's state, a later part's local chain from zero and its
     // transition chain from the identity
     const float* state_in = !seg_first ? carry + carry_tile : (part == 0 && a.initial_state ? a.initial_state + tile : nullptr);
     float* state_out = seg_last ? (a.final_state ? a.final_state + tile : nullptr) : carry + carry_tile;
     if (phi && seg_first) {
 #pragma unroll
-      for (int w = 0; w < 32; ++w)
-        Hreg[w] = make_float2(64 * grp + 2 * w == d ? 1.f : 0.f, 64 * grp + 2 * w + 1 == d ? 1.f : 0.f);
+      for (int w = 0; w < HC / 2; ++w)
+        Hreg[w] = make_float2(HC * grp + 2 * w == d ? 1.f : 0.f, HC * grp + 2 * w + 1 == d ? 1.f : 0.f);
     } else if (state_in != nullptr) {
 #pragma unroll
-      for (int w = 0; w < 32; ++w)
-        Hreg[w] = make_float2(state_in[(int64_t)(64 * grp + 2 * w) * D + d], state_in[(int64_t)(64 * grp + 2 * w + 1) * D + d]);
+      for (int w = 0; w < HC / 2; ++w)
+        Hreg[w] = make_float2(state_in[(int64_t)(HC * grp + 2 * w) * D + d], state_in[(int64_t)(HC * grp + 2 * w + 1) * D + d]);
     } else {
 #pragma unroll
-      for (int w = 0; w < 32; ++w) Hreg[w] = make_float2(0.f, 0.f);
+      for (int w = 0; w < HC / 2; ++w) Hreg[w] = make_float2(0.f, 0.f);
     }
     auto publish_h = [&]() {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int part16 = 0; part16 < HC / 32; ++part16) {  // 16 packed words (32 columns of H) at a time
         uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int w = 0; w < 16; ++w) split_pair(Hreg[16 * half + w], hi[w], lo[w]);
-        tc::tmem_st16(lane_addr + TM_HHI + 32 * grp + 16 * half, hi);
-        tc::tmem_st16(lane_addr + TM_HLO + 32 * grp + 16 * half, lo);
+        for (int w = 0; w < 16; ++w) split_pair(Hreg[16 * part16 + w], hi[w], lo[w]);
+        tc::tmem_st16(lane_addr + TM_HHI + (HC / 2) * grp + 16 * part16, hi);
+        tc::tmem_st16(lane_addr + TM_HLO + (HC / 2) * grp + 16 * part16, lo);
       }
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
@@ -956,84 +995,83 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       const int s = c & 1;
       const uint32_t cp = (uint32_t)c & 1u, u = (uint32_t)(c >> 1);
       const float* scal = reinterpret_cast<const float*>(smem + OFF_SCAL + (c & 3) * SCAL_BYTES);
-      if (!tc::mbar_wait_warp(&full[s], u & 1u, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait_warp(&pfull[s], u & 1u, abort_flag)) { alive = false; break; }  // the scale vectors
       if (!tc::mbar_wait_warp(vn_full, cp, abort_flag)) { alive = false; break; }
       tc::tc_fence_after_sync();
       {
-        uint32_t acc[32];
-        tc::tmem_ld32(lane_addr + TM_VN + 32 * grp, acc);
-        float2 v[16];
+        uint32_t acc[VC];
+        tc::tmem_ld_n<VC>(lane_addr + TM_VN + VC * grp, acc);
+        float2 v[VC / 2];
         tc::tmem_ld_wait();
 #pragma unroll
-        for (int w = 0; w < 16; ++w) v[w] = make_float2(__uint_as_float(acc[2 * w]), __uint_as_float(acc[2 * w + 1]));
+        for (int w = 0; w < VC / 2; ++w) v[w] = make_float2(__uint_as_float(acc[2 * w]), __uint_as_float(acc[2 * w + 1]));
         {  // Vd first: its columns alias nothing, and the state update waits only for it
-          uint32_t dh[16], dl[16];
+          uint32_t dh[VC / 2], dl[VC / 2];
 #pragma unroll
-          for (int w = 0; w < 16; ++w) {
-            const float2 ks = *reinterpret_cast<const float2*>(scal + C + 32 * grp + 2 * w);
+          for (int w = 0; w < VC / 2; ++w) {
+            const float2 ks = *reinterpret_cast<const float2*>(scal + C + VC * grp + 2 * w);
             split_pair(__fmul2_rn(v[w], ks), dh[w], dl[w]);
           }
-          tc::tmem_st16(lane_addr + TM_VDHI + 16 * grp, dh);
-          tc::tmem_st16(lane_addr + TM_VDLO + 16 * grp, dl);
+          tc::tmem_st_n<VC / 2>(lane_addr + TM_VN + VC * grp, dh);  // into this warp's own accumulator columns
+          tc::tmem_st_n<VC / 2>(lane_addr + TM_VN + VC * grp + VC / 2, dl);
           tc::tmem_st_wait();
           tc::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(vd_ready);
         }
-        // both groups have read the accumulator before its columns are reused for Vn hi/lo
-        if (!group_sync(chain_bar, sync_phase, lane, abort_flag)) { alive = false; break; }
+        // the Vn images have columns of their own, free once O2 of the previous chunk is complete (long ago)
+        if (!tc::mbar_wait_warp(o_full, cp ^ 1u, abort_flag)) { alive = false; break; }
         {
-          uint32_t vh[16], vl[16];
+          uint32_t vh[VC / 2], vl[VC / 2];
 #pragma unroll
-          for (int w = 0; w < 16; ++w) split_pair(v[w], vh[w], vl[w]);
-          tc::tmem_st16(lane_addr + TM_VNHI + 16 * grp, vh);
-          tc::tmem_st16(lane_addr + TM_VNLO + 16 * grp, vl);
+          for (int w = 0; w < VC / 2; ++w) split_pair(v[w], vh[w], vl[w]);
+          tc::tmem_st_n<VC / 2>(lane_addr + TM_VNHI + (VC / 2) * grp, vh);
+          tc::tmem_st_n<VC / 2>(lane_addr + TM_VNLO + (VC / 2) * grp, vl);
           tc::tmem_st_wait();
           tc::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(vn_ready);
         }
       }
-      if (!tc::mbar_wait_warp(dh_full, cp, abort_flag)) { alive = false; break; }
+      if (!tc::mbar_wait2(dh_full, cp, o1_done, cp, abort_flag)) { alive = false; break; }
       tc::tc_fence_after_sync();
       {
         const float decay = scal[2 * C];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int part32 = 0; part32 < HC / 32; ++part32) {
           uint32_t dh[32];
-          tc::tmem_ld32(lane_addr + TM_DH + 64 * grp + 32 * half, dh);
+          tc::tmem_ld32(lane_addr + TM_DH + HC * grp + 32 * part32, dh);
           tc::tmem_ld_wait();
 #pragma unroll
           for (int w = 0; w < 16; ++w)
-            Hreg[16 * half + w] = __ffma2_rn(make_float2(decay, decay), Hreg[16 * half + w],
-                                             make_float2(__uint_as_float(dh[2 * w]), __uint_as_float(dh[2 * w + 1])));
+            Hreg[16 * part32 + w] = __ffma2_rn(make_float2(decay, decay), Hreg[16 * part32 + w],
+                                               make_float2(__uint_as_float(dh[2 * w]), __uint_as_float(dh[2 * w + 1])));
         }
         publish_h();
       }
-      if (lane == 0) tc::mbar_arrive(&empty[s]);  // this warp no longer reads the stage's scale vectors
     }
     if (alive && state_out != nullptr) {
 #pragma unroll
-      for (int w = 0; w < 32; ++w) {
-        state_out[(int64_t)(64 * grp + 2 * w) * D + d] = Hreg[w].x;
-        state_out[(int64_t)(64 * grp + 2 * w + 1) * D + d] = Hreg[w].y;
+      for (int w = 0; w < HC / 2; ++w) {
+        state_out[(int64_t)(HC * grp + 2 * w) * D + d] = Hreg[w].x;
+        state_out[(int64_t)(HC * grp + 2 * w + 1) * D + d] = Hreg[w].y;
       }
     }
     if (alive && multi && chain == 0 && c_hi == part_end) {
-      // the state that enters part 1, as the fix-up's B operand image (row = d_v, K = d_k): this thread's row, 8 pieces
+      // the state that enters part 1, as the fix-up's B operand image (row = d_v, K = d_k): this thread's row, HC / 8 pieces
       uint8_t* img = m0_pack + (((int64_t)n * (plan.parts - 1)) * a.Hv + h) * (int64_t)PACK_BYTES;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < HC / 8; ++j) {
         uint32_t hi[4], lo[4];
 #pragma unroll
         for (int w = 0; w < 4; ++w) split_pair(Hreg[4 * j + w], hi[w], lo[w]);
-        const uint32_t off = kmajor_piece_off(d, 8 * grp + j);
+        const uint32_t off = kmajor_piece_off(d, (HC / 8) * grp + j);
         *reinterpret_cast<uint4*>(img + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<uint4*>(img + D * D * 2 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
     }
   } else {
-    tc::reg_set<REGS_OUT, 128>();
+    tc::reg_set<REGS_OUT, REGS_LAUNCH>();
     // ------------------------------------------------------------------ output warps: o = scale (qs_i O1 + O2), straight
     // from registers: thread = d_v row, one store per token (a warp covers 32 adjacent features of one token).  When a
     // gated norm follows, the un-normalised output is kept in fp32 scratch for the norm kernel; otherwise it is the result.
@@ -1054,30 +1092,34 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       float* pf = of ? of + tok0 * ((int64_t)a.Hv * D) : nullptr;
       __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
       const int64_t fstep = (int64_t)a.Hv * D, bstep = a.o_stride_t;
-      constexpr int PW = kMulti ? 16 : 32;  // tokens per piece
+      // O1 is taken whole and released at once: O1 of the next chunk is the first thing the tensor pipe runs while the
+      // chain epilogue converts Vn, and must not wait for the stores below.  O2 follows in pieces.
+      uint32_t o1[C];
+      tc::tmem_ld32(lane_addr + TM_O1, reinterpret_cast<uint32_t(&)[32]>(o1[0]));
+      tc::tmem_ld32(lane_addr + TM_O1 + 32, reinterpret_cast<uint32_t(&)[32]>(o1[32]));
+      tc::tmem_ld_wait();
+      tc::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(o1_empty);
+      constexpr int PW = 16;  // tokens per piece
 #pragma unroll
       for (int piece = 0; piece < C / PW; ++piece) {
-        uint32_t o1[PW], o2[PW];
-        if constexpr (PW == 16) {
-          tc::tmem_ld16(lane_addr + TM_O1 + PW * piece, o1);
-          tc::tmem_ld16(lane_addr + TM_O2 + PW * piece, o2);
-        } else {
-          tc::tmem_ld32(lane_addr + TM_O1 + PW * piece, o1);
-          tc::tmem_ld32(lane_addr + TM_O2 + PW * piece, o2);
-        }
+        uint32_t o2[PW];
+        tc::tmem_ld16(lane_addr + TM_O2 + PW * piece, o2);
         tc::tmem_ld_wait();
-        if (piece == C / PW - 1) {  // both accumulators are in registers: the next chunk's MMAs may overwrite them
+        if (piece == C / PW - 1) {  // the accumulator is in registers: the next chunk's MMAs may overwrite it
           tc::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive(o_empty);
+          if (lane == 0) tc::mbar_arrive(o2_empty);
         }
         float ov[PW];
 #pragma unroll
         for (int j4 = 0; j4 < PW / 4; ++j4) {
-          const float4 qs = *reinterpret_cast<const float4*>(scal + PW * piece + 4 * j4);
-          const float2 r0 = __ffma2_rn(make_float2(qs.x, qs.y), make_float2(__uint_as_float(o1[4 * j4]), __uint_as_float(o1[4 * j4 + 1])),
+          const int j = PW * piece + 4 * j4;
+          const float4 qs = *reinterpret_cast<const float4*>(scal + j);
+          const float2 r0 = __ffma2_rn(make_float2(qs.x, qs.y), make_float2(__uint_as_float(o1[j]), __uint_as_float(o1[j + 1])),
                                        make_float2(__uint_as_float(o2[4 * j4]), __uint_as_float(o2[4 * j4 + 1])));
-          const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[4 * j4 + 2]), __uint_as_float(o1[4 * j4 + 3])),
+          const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[j + 2]), __uint_as_float(o1[j + 3])),
                                        make_float2(__uint_as_float(o2[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 3])));
           ov[4 * j4 + 0] = r0.x; ov[4 * j4 + 1] = r0.y; ov[4 * j4 + 2] = r1.x; ov[4 * j4 + 3] = r1.y;
         }

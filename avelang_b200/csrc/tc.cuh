@@ -43,6 +43,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// Bounded waits for two or three phases at once.  The polls are independent, so the latencies of phases that are
+// already complete overlap instead of adding up.
+__device__ __forceinline__ bool mbar_wait2(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, volatile uint32_t* abort_flag) {
+  bool d0 = false, d1 = false;
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    const bool n0 = d0 || mbar_try_wait(b0, p0), n1 = d1 || mbar_try_wait(b1, p1);
+    d0 = n0; d1 = n1;
+    if (d0 && d1) return true;
+    if ((it & 63u) == 63u && *abort_flag != 0u) return false;
+  }
+  *abort_flag = 1u;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait3(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2,
+                                           volatile uint32_t* abort_flag) {
+  bool d0 = false, d1 = false, d2 = false;
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    const bool n0 = d0 || mbar_try_wait(b0, p0), n1 = d1 || mbar_try_wait(b1, p1), n2 = d2 || mbar_try_wait(b2, p2);
+    d0 = n0; d1 = n1; d2 = n2;
+    if (d0 && d1 && d2) return true;
+    if ((it & 63u) == 63u && *abort_flag != 0u) return false;
+  }
+  *abort_flag = 1u;
+  return false;
+}
+
 // Bounded wait called by all 32 lanes of a converged warp.  Every lane polls: letting lane 0 poll alone and
 // broadcasting the outcome was measured and doubled the time of the scan (0.90 ms against 0.46 ms on an 8192-token
 // sequence), so the hand-off latency is not a matter of the number of pollers.
@@ -204,7 +230,23 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// N consecutive 32-bit columns of this warp's 32 lanes
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 16 || N == 32, "column count");
+  if constexpr (N == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_n(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16, "column count");
+  if constexpr (N == 16) tmem_st16(taddr, r); else tmem_st8(taddr, r);
+}
 
 }  // namespace tc
 
