@@ -737,7 +737,7 @@ def main():
             "clocks": clocks}
     achieved = flops / (ms * 1e-3) / 1e12
     line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                        "frac": achieved / peaks["bf16_tflops"], "traffic": 471_699_248,
+                        "frac": achieved / peaks["bf16_tflops"], "traffic": 469_767_936,
                         "traffic_source": "profiles/prefill_config1_launch_list.md: DRAM bytes read + written by the four "
                                           "chunk_scan launches of one step (the dominant kernel), ncu with its "
                                           "cache flush between kernels; algorithmic bytes of the step are in hbm_view",
