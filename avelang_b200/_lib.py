@@ -15,7 +15,7 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, MISALIGNED, CUDA_ERROR, WORKSPACE_TOO_SMALL =
 DEV_BAD_SLOT, DEV_BAD_SEQLEN, DEV_WAIT_EXPIRED = 1, 2, 4
 FLAG_QK_L2NORM, FLAG_GATE_FIRST = 1, 2
 NOALLOC_SCRATCH_BYTES = 64 << 20
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class GdnArgs(ctypes.Structure):
@@ -39,6 +39,12 @@ class NormArgs(ctypes.Structure):
 class GemmArgs(ctypes.Structure):
     _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("c", P),
                 ("M", I64), ("N", I64), ("K", I64), ("lda", I64), ("ldb", I64), ("ldc", I64), ("status", P)]
+
+
+class GemmReduceArgs(ctypes.Structure):
+    _fields_ = [("struct_size", U32), ("flags", U32), ("a", P), ("b", P), ("M", I64), ("N", I64), ("K", I64),
+                ("lda", I64), ("ldb", I64), ("stage_peers", P), ("stage", P), ("out_peers", P), ("ldc", I64),
+                ("n_ranks", I32), ("rank", I32), ("rows_per_owner", I64), ("status", P)]
 
 
 class ConvArgs(ctypes.Structure):
@@ -86,6 +92,8 @@ SYMBOLS = {
     "ave_gdn_decode_step": (ctypes.c_int, [ctypes.POINTER(GdnArgs), P]),
     "ave_gdn_gated_rmsnorm": (ctypes.c_int, [ctypes.POINTER(NormArgs), P]),
     "ave_gemm_bf16_nt": (ctypes.c_int, [ctypes.POINTER(GemmArgs), P]),
+    "ave_gemm_bf16_nt_scatter": (ctypes.c_int, [ctypes.POINTER(GemmReduceArgs), P]),
+    "ave_gemm_reduce_push": (ctypes.c_int, [ctypes.POINTER(GemmReduceArgs), P]),
     "ave_gdn_conv1d_silu": (ctypes.c_int, [ctypes.POINTER(ConvArgs), P]),
     "ave_gdn_conv1d_update": (ctypes.c_int, [ctypes.POINTER(ConvUpdateArgs), P]),
     "ave_gdn_gate_beta": (ctypes.c_int, [ctypes.POINTER(GateArgs), P]),

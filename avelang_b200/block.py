@@ -122,10 +122,20 @@ class GdnBlockShard:
         full, peers = self._symmetric_output(B, T, x.device, group)
         hl = self.hv_local
         mine = full[:, :, self.shard.rank * hl:(self.shard.rank + 1) * hl]
-        dist.barrier(group)   # every rank is done reading the previous contents of the buffers
+        self._stream_barrier(group)   # every rank is done reading the previous contents of the buffers
         self.forward_local(x, cu_seqlens, out=mine, out_peers=peers)
-        dist.barrier(group)   # every rank's stores have landed
+        self._stream_barrier(group)   # every rank's stores have landed
         return full
+
+    def _stream_barrier(self, group=None):
+        """Cross-rank barrier in stream order: a one-element all-reduce on the current stream.  What follows it on this
+        rank's stream runs after everything every rank enqueued before its own call; unlike ``dist.barrier`` the host
+        does not wait, so the launches on either side stay queued back to back."""
+        import torch.distributed as dist
+        tok = self.__dict__.get("_barrier_token")
+        if tok is None:
+            tok = self.__dict__["_barrier_token"] = torch.zeros(1, dtype=torch.int32, device=self.w.device)
+        dist.all_reduce(tok, group=group)
 
     def _symmetric_output(self, B, T, device, group):
         """Output buffer [B, T, Hv, dv] in symmetric memory plus the device array of every rank's base address for this
@@ -162,16 +172,54 @@ class GdnBlockTP(GdnBlockShard):
         cols = output_projection_columns(self.shard, dv)
         self.w_out = w_out[:, cols].to(torch.bfloat16).to(device).contiguous()  # [hidden, hl*dv]
 
-    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cu_seqlens=None, group=None, fused_reduce=False) -> torch.Tensor:
         """Returns the block output after the output projection, ``[B, T, hidden]`` bf16, identical on every rank."""
-        from . import gemm
         B, T, _ = x.shape
         o = self.forward_local(x, cu_seqlens)                                   # [B, T, hl, dv]
-        part = gemm.gemm_pipeline_transposed_b(o.reshape(B * T, -1), self.w_out)  # [B*T, hidden], this rank's partial sum
-        if self.shard.world > 1:
-            import torch.distributed as dist
-            dist.all_reduce(part, group=group)
-        return part.reshape(B, T, -1)
+        return self.project(o.reshape(B * T, -1), group, fused_reduce).reshape(B, T, -1)
+
+    def project(self, o2d: torch.Tensor, group=None, fused_reduce=False) -> torch.Tensor:
+        """Output projection of this rank's normalised head outputs ``[M, hl*dv]`` and the sum over ranks, ``[M, hidden]``.
+        Default: this rank's partial product, then one NCCL all-reduce.  ``fused_reduce=True``: the GEMM's epilogue stores
+        each row of the partial product into the staging buffer of the rank that owns the row (symmetric memory, plain
+        peer stores over NVLink, under the next tile's main loop); after a barrier every owner sums its rows in fp32 and
+        stores them into every rank's result; a last barrier.  The fused result lives in a cached symmetric buffer that
+        the next fused call overwrites."""
+        from . import gemm
+        if not fused_reduce or self.shard.world == 1:
+            part = gemm.gemm_pipeline_transposed_b(o2d, self.w_out)              # this rank's partial sum
+            if self.shard.world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(part, group=group)
+            return part
+        stage, stage_peers, out, out_peers = self._symmetric_projection(o2d.shape[0], o2d.device, group)
+        self._stream_barrier(group)   # every rank has consumed the previous result and its staging slots
+        gemm.gemm_scatter_to_owners(o2d, self.w_out, stage, stage_peers, self.shard.rank)
+        self._stream_barrier(group)   # every rank's partial rows have landed at their owners
+        gemm.reduce_push_to_all(stage, out_peers, out, self.shard.rank)
+        self._stream_barrier(group)   # every owner's rows have landed everywhere
+        return out
+
+    def _symmetric_projection(self, M, device, group):
+        """Staging buffer [world, rows_per_owner, hidden] and result [M, hidden] in symmetric memory, with the device
+        arrays of every rank's addresses; cached per M."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        key = ("proj", M, str(device))
+        cache = self.__dict__.setdefault("_symm_cache", {})
+        if key not in cache:
+            grp = group if group is not None else dist.group.WORLD
+            world, hidden = self.shard.world, self.w_out.shape[0]
+            rpo = (M + world - 1) // world
+            stage = symm.empty((world, rpo, hidden), dtype=torch.bfloat16, device=device)
+            h1 = symm.rendezvous(stage, grp)
+            out = symm.empty((M, hidden), dtype=torch.bfloat16, device=device)
+            h2 = symm.rendezvous(out, grp)
+            sp = torch.tensor([int(p) for p in h1.buffer_ptrs], dtype=torch.int64, device=device)
+            op = torch.tensor([int(p) for p in h2.buffer_ptrs], dtype=torch.int64, device=device)
+            cache[key] = (stage, sp, out, op, h1, h2)
+        stage, sp, out, op, _, _ = cache[key]
+        return stage, sp, out, op
 
 
 def gather_heads(o_local: torch.Tensor, world: int, group=None) -> torch.Tensor:

@@ -16,6 +16,8 @@ int launch_conv1d_silu(const AveConvArgs& a, cudaStream_t stream);
 int launch_gate_beta(const AveGateArgs& a, cudaStream_t stream);
 int launch_conv1d_update(const AveConvUpdateArgs& a, cudaStream_t stream);
 int launch_gemm_bf16_nt(const AveGemmArgs& a, cudaStream_t stream);
+int launch_gemm_bf16_nt_scatter(const AveGemmReduceArgs& a, cudaStream_t stream);
+int launch_gemm_reduce_push(const AveGemmReduceArgs& a, cudaStream_t stream);
 int launch_decode_layer(const AveGdnDecodeLayerArgs& a, cudaStream_t stream);
 int launch_backward(const AveGdnBwdArgs& a, cudaStream_t stream);
 size_t backward_workspace_bytes(const AveGdnBwdArgs& a);
@@ -206,6 +208,32 @@ int ave_gemm_bf16_nt(const AveGemmArgs* a, void* stream) {
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->c) || (a->lda % 8) || (a->ldb % 8) || (a->ldc % 8)) return AVE_GDN_MISALIGNED;
   if (a->K % 8 || a->K == 0) return AVE_GDN_UNSUPPORTED;
   return launch_gemm_bf16_nt(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int validate_gemm_reduce(const AveGemmReduceArgs* a) {
+  if (a == nullptr || a->struct_size != sizeof(AveGemmReduceArgs) || a->M < 0 || a->N < 0 || a->K < 0) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->n_ranks < 1 || a->n_ranks > 64 || a->rank < 0 || a->rank >= a->n_ranks) return AVE_GDN_INVALID_ARGUMENT;
+  if (a->rows_per_owner <= 0 || a->rows_per_owner * a->n_ranks < a->M) return AVE_GDN_INVALID_ARGUMENT;
+  if (!a->stage_peers || !a->stage || !a->out_peers) return AVE_GDN_INVALID_ARGUMENT;
+  if (!aligned16(a->stage) || (a->N % 8) || (a->ldc % 8) || a->ldc < a->N) return AVE_GDN_MISALIGNED;
+  return AVE_GDN_OK;
+}
+
+int ave_gemm_bf16_nt_scatter(const AveGemmReduceArgs* a, void* stream) {
+  const int rc = validate_gemm_reduce(a);
+  if (rc != AVE_GDN_OK) return rc;
+  if (a->M == 0 || a->N == 0) return AVE_GDN_OK;
+  if (!a->a || !a->b) return AVE_GDN_INVALID_ARGUMENT;
+  if (!aligned16(a->a) || !aligned16(a->b) || (a->lda % 8) || (a->ldb % 8)) return AVE_GDN_MISALIGNED;
+  if (a->K % 8 || a->K == 0) return AVE_GDN_UNSUPPORTED;
+  return launch_gemm_bf16_nt_scatter(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ave_gemm_reduce_push(const AveGemmReduceArgs* a, void* stream) {
+  const int rc = validate_gemm_reduce(a);
+  if (rc != AVE_GDN_OK) return rc;
+  if (a->M == 0 || a->N == 0) return AVE_GDN_OK;
+  return launch_gemm_reduce_push(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

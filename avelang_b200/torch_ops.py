@@ -24,6 +24,8 @@ SCHEMAS = {
     "conv1d_update": "(Tensor x, Tensor(a!) conv_state, Tensor weight, Tensor? bias, Tensor? state_indices, Tensor(b!) out) -> ()",
     "gate_beta": "(Tensor a, Tensor b, Tensor A_log, Tensor dt_bias, Tensor(a!) g, Tensor(b!) beta) -> ()",
     "gemm_bf16_nt": "(Tensor A, Tensor B, Tensor(a!) out) -> ()",
+    "gemm_scatter": "(Tensor A, Tensor B, Tensor(a!) stage, Tensor stage_peers, int rank, int rows_per_owner) -> ()",
+    "gemm_reduce_push": "(Tensor stage, Tensor out_peers, Tensor(a!) out, int rank, int M, int rows_per_owner) -> ()",
     "recurrent_backward": "(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor d_o, float scale, Tensor? initial_state, "
                           "Tensor? d_final_state, Tensor? cu_seqlens, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) dg, "
                           "Tensor(e!) dbeta, Tensor(f!)? d_initial_state) -> ()",

@@ -535,6 +535,26 @@ def bench_block(args, rank, world, steps=None, full_line=True):
         d_paths = float((y.float() - res["y_nccl"].float()).norm() / res["y_nccl"].float().norm()) if fused else None
         extra = {"nccl_gather_ms_per_step": nccl_ms, "fused_equals_nccl": bool(torch.equal(y, res["y_nccl"])) if fused else None,
                  "fused_vs_nccl_rel_l2": d_paths, "fused_vs_nccl_gate": 2e-3}
+    if world > 1:
+        # The tensor-parallel form's output projection [B*T, Hv*dv / world] x [hidden, Hv*dv / world]^T with its sum over
+        # ranks: own GEMM + one NCCL all-reduce, against the GEMM whose epilogue stores each row at its owner (peer
+        # stores) followed by the owners' sum-and-store kernel.  Timed on this rank's normalised head outputs.
+        from avelang_b200.block import GdnBlockTP
+        w_out = (0.05 * torch.randn(hidden, HV * D, generator=gen)).bfloat16()
+        tp = GdnBlockTP(w_in, conv_w, A_log, dt_bias, norm_w, w_out, Hk=HK, Hv=HV, dk=D, dv=D, rank=rank, world=world)
+        o2d = blk.forward_local(x).reshape(B * T, -1)
+        pr = {}
+        def proj_nccl():
+            pr["nccl"] = tp.project(o2d)
+        def proj_fused():
+            pr["fused"] = tp.project(o2d, fused_reduce=True)
+        p_nccl = max_over_ranks(time_steps(proj_nccl, steps, args.warmup, world, flush), world) / steps
+        p_fused = max_over_ranks(time_steps(proj_fused, steps, args.warmup, world, flush), world) / steps
+        d_proj = float((pr["fused"].float() - pr["nccl"].float()).norm() / pr["nccl"].float().norm())
+        extra["out_projection"] = {"gemm_then_nccl_all_reduce_ms": p_nccl, "gemm_with_fused_sum_ms": p_fused,
+                                   "fused_vs_nccl_rel_l2": d_proj, "gate": 1e-2,
+                                   "shape": f"M={B * T}, N={hidden}, K={HV * D // world} per rank"}
+        del o2d, pr, tp
     # parity 1: causal prefix of batch row 2, every head (they come from every rank), end to end
     P = 160
     ref = gdn_oracle.gdn_block_ref(x_cpu[2:3, :P], w_in, conv_w, A_log, dt_bias, norm_w, Hk=HK, Hv=HV, dk=D, dv=D)
@@ -555,7 +575,8 @@ def bench_block(args, rank, world, steps=None, full_line=True):
                          f"and convolution outputs differ from the reference's by a rounding in a few per cent of elements); "
                          f"delta rule + gated norm on {Pd} tokens of batch row 1, every rank's heads, vs the fp64 C checker "
                          "fed the device's own stage inputs (1e-3)",
-              "ok": bool(e_block <= 5e-3 and e_stage <= 1e-3 and st == 0 and (extra.get("fused_vs_nccl_rel_l2") or 0.0) <= 2e-3)}
+              "ok": bool(e_block <= 5e-3 and e_stage <= 1e-3 and st == 0 and (extra.get("fused_vs_nccl_rel_l2") or 0.0) <= 2e-3
+                         and extra.get("out_projection", {}).get("fused_vs_nccl_rel_l2", 0.0) <= 1e-2)}
     flops = 2 * B * T * hidden * n_out + (B * T // 64) * HV * FLOP_PER_CHUNK_HEAD
     peaks = measured_peaks()
     achieved = flops / (ms * 1e-3) / 1e12

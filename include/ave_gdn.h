@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define AVE_GDN_ABI_VERSION 3
+#define AVE_GDN_ABI_VERSION 4
 
 typedef enum AveGdnStatus {
   AVE_GDN_OK = 0,
@@ -161,6 +161,35 @@ typedef struct AveGemmArgs {
   uint32_t* status;      /* optional device status word (AVE_GDN_DEV_WAIT_EXPIRED: tiles were abandoned, C is incomplete) */
 } AveGemmArgs;
 int ave_gemm_bf16_nt(const AveGemmArgs* args, void* stream);
+
+/* Row-parallel linear layer with the cross-rank sum fused into the GEMM (the output projection of the tensor-parallel
+ * block: each rank holds the K slice of its own heads; the reference convention for such a function is the
+ * tensor-in/tensor-out GEMM of python/avelang_kernels/amdgpu_gemm.py:458-494, the sum replaces the all-reduce a caller
+ * would add behind it).  Two calls with a cross-rank barrier between them and one after:
+ *   ave_gemm_bf16_nt_scatter  C_partial = A * B^T; the GEMM's epilogue stores each row, as bf16, straight into slot
+ *                             `rank` of the staging buffer of the rank that owns the row (rows_per_owner consecutive
+ *                             rows per rank) -- plain peer stores, tile by tile, under the next tile's main loop;
+ *   ave_gemm_reduce_push      the owner sums its rows over the n_ranks slots in fp32, in slot order, rounds once to
+ *                             bf16 and stores them into every rank's result matrix [M][ldc].
+ * stage_peers / out_peers: device arrays of n_ranks addresses (this rank's own included) of buffers every rank can
+ * reach (peer-mapped or symmetric memory); each staging buffer holds n_ranks * rows_per_owner * N bf16.  N % 8 == 0. */
+typedef struct AveGemmReduceArgs {
+  uint32_t struct_size;
+  uint32_t flags;
+  const void* a;
+  const void* b;
+  int64_t M, N, K;
+  int64_t lda, ldb;
+  const void* const* stage_peers;
+  void* stage;                   /* this rank's own staging buffer */
+  const void* const* out_peers;
+  int64_t ldc;                   /* row stride of the result matrices, elements, multiple of 8 */
+  int32_t n_ranks, rank;
+  int64_t rows_per_owner;        /* >= ceil(M / n_ranks) */
+  uint32_t* status;
+} AveGemmReduceArgs;
+int ave_gemm_bf16_nt_scatter(const AveGemmReduceArgs* args, void* stream);
+int ave_gemm_reduce_push(const AveGemmReduceArgs* args, void* stream);
 
 /* Depthwise causal conv over time (kernel width 2..4) followed by SiLU, zero history at each sequence
  * start.  x,y [B,T,C] bf16, w [C,width] bf16, optional bias [C] bf16, optional cu_seqlens (B == 1). */

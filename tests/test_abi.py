@@ -31,23 +31,25 @@ def test_exports_every_declared_symbol(built_lib):
 
 def test_struct_mirrors_match_header(tmp_path):
     src = tmp_path / "sz.c"
-    src.write_text('#include "ave_gdn.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include "ave_gdn.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(AveGdnArgs),sizeof(AveGdnNormArgs),sizeof(AveGemmArgs),sizeof(AveConvArgs),sizeof(AveGateArgs),"
                    "offsetof(AveGdnArgs,scale),offsetof(AveGdnArgs,q_stride_b),sizeof(AveConvUpdateArgs),sizeof(AveGdnDecodeLayerArgs),"
-                   "offsetof(AveGdnDecodeLayerArgs,proj_stride),offsetof(AveGemmArgs,status));return 0;}\n")
+                   "offsetof(AveGdnDecodeLayerArgs,proj_stride),offsetof(AveGemmArgs,status),sizeof(AveGemmReduceArgs),"
+                   "offsetof(AveGemmReduceArgs,rows_per_owner));return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     want = [ctypes.sizeof(_lib.GdnArgs), ctypes.sizeof(_lib.NormArgs), ctypes.sizeof(_lib.GemmArgs),
             ctypes.sizeof(_lib.ConvArgs), ctypes.sizeof(_lib.GateArgs), _lib.GdnArgs.scale.offset,
             _lib.GdnArgs.q_stride_b.offset, ctypes.sizeof(_lib.ConvUpdateArgs), ctypes.sizeof(_lib.DecodeLayerArgs),
-            _lib.DecodeLayerArgs.proj_stride.offset, _lib.GemmArgs.status.offset]
+            _lib.DecodeLayerArgs.proj_stride.offset, _lib.GemmArgs.status.offset, ctypes.sizeof(_lib.GemmReduceArgs),
+            _lib.GemmReduceArgs.rows_per_owner.offset]
     assert got == want
 
 
 def test_status_codes_without_a_device(built_lib):
     lib = _lib.load()
-    assert lib.ave_gdn_abi_version() == _lib.ABI_VERSION == 3
+    assert lib.ave_gdn_abi_version() == _lib.ABI_VERSION == 4
     assert lib.ave_gdn_status_string(0) == b"ok"
     a = _lib.GdnArgs()
     assert lib.ave_gdn_decode_step(ctypes.byref(a), None) == _lib.INVALID_ARGUMENT  # struct_size == 0
@@ -88,6 +90,11 @@ def test_status_codes_without_a_device(built_lib):
     g.struct_size = ctypes.sizeof(_lib.GemmArgs)
     g.M, g.N, g.K = 128, 128, 64
     assert lib.ave_gemm_bf16_nt(ctypes.byref(g), None) == _lib.INVALID_ARGUMENT
+    r = _lib.GemmReduceArgs()
+    r.struct_size = ctypes.sizeof(_lib.GemmReduceArgs)
+    r.M, r.N, r.K, r.n_ranks, r.rank, r.rows_per_owner = 256, 128, 64, 2, 0, 64  # two owners of 64 rows cannot hold 256
+    assert lib.ave_gemm_bf16_nt_scatter(ctypes.byref(r), None) == _lib.INVALID_ARGUMENT
+    assert lib.ave_gemm_reduce_push(ctypes.byref(r), None) == _lib.INVALID_ARGUMENT
 
 
 def test_status_maps_to_reference_exceptions(built_lib):
