@@ -1093,7 +1093,7 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       __nv_bfloat16* pb = og + tok0 * a.o_stride_t + d;
       const int64_t fstep = (int64_t)a.Hv * D, bstep = a.o_stride_t;
       // O1 is taken whole and released at once: O1 of the next chunk is the first thing the tensor pipe runs while the
-      // chain epilogue converts Vn, and must not wait for the stores below.  O2 follows in pieces.
+      // chain epilogue converts Vn, and must not wait for the stores below.
       uint32_t o1[C];
       tc::tmem_ld32(lane_addr + TM_O1, reinterpret_cast<uint32_t(&)[32]>(o1[0]));
       tc::tmem_ld32(lane_addr + TM_O1 + 32, reinterpret_cast<uint32_t(&)[32]>(o1[32]));
@@ -1101,6 +1101,8 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(o1_empty);
+      // O2 follows in pieces and is folded into the registers that hold O1 (o = qs O1 + O2), so both accumulators are
+      // free before the first store: how fast the stores drain no longer decides when the next chunk's output MMAs may run.
       constexpr int PW = 16;  // tokens per piece
 #pragma unroll
       for (int piece = 0; piece < C / PW; ++piece) {
@@ -1112,7 +1114,6 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o2_empty);
         }
-        float ov[PW];
 #pragma unroll
         for (int j4 = 0; j4 < PW / 4; ++j4) {
           const int j = PW * piece + 4 * j4;
@@ -1121,8 +1122,14 @@ chunk_scan_tc_kernel(const AveGdnArgs a, const __grid_constant__ GdnMaps maps, c
                                        make_float2(__uint_as_float(o2[4 * j4]), __uint_as_float(o2[4 * j4 + 1])));
           const float2 r1 = __ffma2_rn(make_float2(qs.z, qs.w), make_float2(__uint_as_float(o1[j + 2]), __uint_as_float(o1[j + 3])),
                                        make_float2(__uint_as_float(o2[4 * j4 + 2]), __uint_as_float(o2[4 * j4 + 3])));
-          ov[4 * j4 + 0] = r0.x; ov[4 * j4 + 1] = r0.y; ov[4 * j4 + 2] = r1.x; ov[4 * j4 + 3] = r1.y;
+          o1[j] = __float_as_uint(r0.x); o1[j + 1] = __float_as_uint(r0.y); o1[j + 2] = __float_as_uint(r1.x); o1[j + 3] = __float_as_uint(r1.y);
         }
+      }
+#pragma unroll
+      for (int piece = 0; piece < C / PW; ++piece) {
+        float ov[PW];
+#pragma unroll
+        for (int j = 0; j < PW; ++j) ov[j] = __uint_as_float(o1[PW * piece + j]);
         const int n_here = min(PW, len - PW * piece);  // tokens of this piece that exist
         if (phi) {
           // qt^T of this chunk as bf16 hi and lo images [128 d_k rows][64 tokens] with the 128-byte swizzle: the fix-up
